@@ -1,0 +1,337 @@
+// Python binding of the native planner runtime.
+//
+// `PlannerEngine` owns everything that lives on the GPU for one planner: the static
+// topology/placement tables, the per-engine workspace and status block, and (when a
+// process group is attached) the peer-memory exchange buffers.  It plays the role of the
+// reference's `CompiledSolver` (reference csrc/plugin.cpp:122-147, :663-679) without a
+// run-time compiler.  The exchange bootstrap mirrors what the reference's `init_comm`
+// does for its intra-node tier (reference csrc/plugin.cpp:395-448): allocate with
+// cudaMalloc, export a CUDA-IPC handle, let Python all-gather the handles through
+// torch.distributed, open the peers' handles and upload a pointer table.
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <c10/cuda/CUDAStream.h>
+#include <pybind11/pybind11.h>
+#include <pybind11/stl.h>
+#include <torch/extension.h>
+
+#include <sstream>
+#include <stdexcept>
+#include <string>
+#include <vector>
+
+#include "planner_api.h"
+
+namespace py = pybind11;
+
+#define LPLB_CHECK(cond, msg)                                   \
+  do {                                                          \
+    if (!(cond)) {                                              \
+      std::ostringstream oss_;                                  \
+      oss_ << "lplb_b200: " << msg << " (" #cond ")";           \
+      throw std::runtime_error(oss_.str());                     \
+    }                                                           \
+  } while (0)
+
+#define LPLB_CUDA(expr)                                                                 \
+  do {                                                                                  \
+    cudaError_t err_ = (expr);                                                          \
+    if (err_ != cudaSuccess) {                                                          \
+      std::ostringstream oss_;                                                          \
+      oss_ << "lplb_b200: " #expr " failed: " << cudaGetErrorName(err_) << ": "        \
+           << cudaGetErrorString(err_);                                                 \
+      throw std::runtime_error(oss_.str());                                             \
+    }                                                                                   \
+  } while (0)
+
+namespace {
+
+struct IpcBlock {
+  // One cudaMalloc'd region: int32 recv[2][n_ranks][E] followed by uint32 flags[n_ranks].
+  void* base = nullptr;
+  size_t bytes = 0;
+};
+
+class PlannerEngine {
+ public:
+  PlannerEngine(int n_group, int g, int d, int ll, int c, int device)
+      : n_group_(n_group), g_(g), d_(d), ll_(ll), c_(c), device_(device) {
+    LPLB_CHECK(g >= 1 && g <= lplb::kMaxGroupSize, "group size must be 1.." << lplb::kMaxGroupSize << ", got " << g);
+    LPLB_CHECK(d >= 1 && d <= lplb::kMaxDup, "replicas per rank must be 1.." << lplb::kMaxDup << ", got " << d);
+    LPLB_CHECK(ll >= c * d, "local logical experts < replicated experts");
+    e_ = n_group * g * ll;
+    LPLB_CHECK(e_ <= lplb::kMaxLogicalExperts, "too many logical experts: " << e_);
+    c10::cuda::CUDAGuard guard(device_);
+    auto opts = torch::TensorOptions().dtype(torch::kInt32).device(torch::kCUDA, device_);
+    const size_t ws_bytes = lplb::planner_workspace_bytes(e_);
+    workspace_ = torch::zeros({(int64_t)((ws_bytes + 3) / 4)}, opts);
+    status_ = torch::zeros({16}, opts);
+    probs_ = torch::zeros({n_group, g, d}, opts.dtype(torch::kFloat32));
+  }
+
+  ~PlannerEngine() {
+    try {
+      close_exchange();
+    } catch (...) {
+    }
+  }
+
+  void set_topology(const torch::Tensor& r2o, const torch::Tensor& o2r) {
+    LPLB_CHECK(r2o.dim() == 2 && r2o.size(0) == g_ && r2o.size(1) == d_, "r2o must be [G, D]");
+    LPLB_CHECK(o2r.sizes() == r2o.sizes(), "o2r must match r2o");
+    r2o_ = to_dev_i32(r2o);
+    o2r_ = to_dev_i32(o2r);
+  }
+
+  void set_mapping(const torch::Tensor& phy2log, const torch::Tensor& log2phy, const torch::Tensor& log2edge) {
+    const int64_t pl = ll_ + c_ * d_;
+    LPLB_CHECK(phy2log.numel() == (int64_t)n_group_ * g_ * pl, "phy2log has the wrong size");
+    LPLB_CHECK(log2phy.dim() == 2 && log2phy.size(0) == e_ && log2phy.size(1) == 2, "log2phy must be [E, 2]");
+    LPLB_CHECK(log2edge.numel() == e_, "log2edge must be [E]");
+    phy2log_ = to_dev_i32(phy2log);
+    log2phy_ = to_dev_i32(log2phy);
+    log2edge_ = to_dev_i32(log2edge);
+  }
+
+  void set_params(int max_iters, double tol, double peer_timeout_us, double grid_timeout_us) {
+    LPLB_CHECK(max_iters >= 1 && max_iters <= 1000, "max_iters out of range");
+    LPLB_CHECK(tol > 0, "tol must be positive");
+    prm_.max_iters = max_iters;
+    prm_.tol = tol;
+    peer_timeout_ns_ = (unsigned long long)(peer_timeout_us * 1e3);
+    grid_timeout_ns_ = (unsigned long long)(grid_timeout_us * 1e3);
+  }
+
+  // ---- stand-alone stages ---------------------------------------------------------
+  std::tuple<torch::Tensor, torch::Tensor> count_idx(const torch::Tensor& idx, int n_cta) {
+    check_idx(idx);
+    LPLB_CHECK(n_cta >= 1, "n_sms must be positive");
+    c10::cuda::CUDAGuard guard(device_);
+    auto by_cta = torch::empty({n_cta, e_}, status_.options());
+    LPLB_CUDA(lplb::launch_count(idx.data_ptr(), idx.scalar_type() == torch::kInt64, idx.numel(), e_, n_cta,
+                                 by_cta.data_ptr<int>(), workspace_.data_ptr(), status_.data_ptr<int>(), stream()));
+    return {by_cta[n_cta - 1], by_cta};
+  }
+
+  std::tuple<torch::Tensor, torch::Tensor> solve(const torch::Tensor& workload, torch::Tensor avail) {
+    require_mapping();
+    LPLB_CHECK(workload.is_cuda() && workload.scalar_type() == torch::kInt32 && workload.is_contiguous(),
+               "workload must be a contiguous int32 CUDA tensor");
+    LPLB_CHECK(workload.numel() == e_, "workload must have " << e_ << " entries, got " << workload.numel());
+    check_avail(avail);
+    c10::cuda::CUDAGuard guard(device_);
+    auto probs = torch::empty({n_group_, g_, d_}, probs_.options());
+    auto normalised = torch::empty({n_group_, g_, ll_}, probs_.options());
+    LPLB_CUDA(lplb::launch_solve(workload.data_ptr<int>(), topo(), prm_, probs.data_ptr<float>(),
+                                 normalised.data_ptr<float>(), avail.data_ptr(),
+                                 avail.scalar_type() == torch::kInt64, status_.data_ptr<int>(), stream()));
+    return {probs, normalised};
+  }
+
+  torch::Tensor map_idx(const torch::Tensor& idx, const torch::Tensor& probs, const torch::Tensor& by_cta, int n_cta) {
+    require_mapping();
+    check_idx(idx);
+    LPLB_CHECK(probs.is_cuda() && probs.scalar_type() == torch::kFloat32 && probs.is_contiguous() &&
+                   probs.numel() == (int64_t)n_group_ * g_ * d_,
+               "o_weight must be a contiguous float32 CUDA tensor with NG*G*D entries");
+    LPLB_CHECK(by_cta.is_cuda() && by_cta.scalar_type() == torch::kInt32 && by_cta.is_contiguous() &&
+                   by_cta.dim() == 2 && by_cta.size(0) == n_cta && by_cta.size(1) == e_,
+               "local_workload_by_sm must be the [n_sms, E] int32 tensor returned by count_workload with the same n_sms");
+    c10::cuda::CUDAGuard guard(device_);
+    auto out = torch::empty_like(idx);
+    LPLB_CUDA(lplb::launch_redirect(idx.data_ptr(), idx.scalar_type() == torch::kInt64, idx.numel(),
+                                    probs.data_ptr<float>(), by_cta.data_ptr<int>(), topo(), n_cta, out.data_ptr(),
+                                    stream()));
+    return out;
+  }
+
+  // Sum a caller-provided int32[E] statistics vector over the peers (NVLink push exchange).
+  torch::Tensor all_reduce_counts(const torch::Tensor& workload) {
+    LPLB_CHECK(exchange_open_, "exchange buffers are not open; call open_exchange first");
+    LPLB_CHECK(workload.is_cuda() && workload.scalar_type() == torch::kInt32 && workload.is_contiguous() &&
+                   workload.numel() == e_,
+               "workload must be a contiguous int32 CUDA tensor with " << e_ << " entries");
+    c10::cuda::CUDAGuard guard(device_);
+    auto out = torch::empty_like(workload);
+    LPLB_CUDA(lplb::launch_exchange(workload.data_ptr<int>(), e_, exchange_desc(), workspace_.data_ptr(),
+                                    out.data_ptr<int>(), status_.data_ptr<int>(), stream()));
+    return out;
+  }
+
+  // ---- single launch ------------------------------------------------------------------
+  torch::Tensor run_fused(const torch::Tensor& idx, torch::Tensor avail, int n_cta, bool use_exchange) {
+    require_mapping();
+    check_idx(idx);
+    check_avail(avail);
+    c10::cuda::CUDAGuard guard(device_);
+    const int is64 = idx.scalar_type() == torch::kInt64;
+    int& limit = is64 ? max_cta64_ : max_cta32_;
+    if (limit < 0) limit = lplb::max_fused_ctas(g_, d_, e_, is64);
+    LPLB_CHECK(limit > 0, "fused kernel cannot be resident on this device");
+    if (n_cta > limit) n_cta = limit;
+    auto out = torch::empty_like(idx);
+    lplb::ExchangeDesc ex{nullptr, nullptr, 1, 0, peer_timeout_ns_};
+    if (use_exchange) {
+      LPLB_CHECK(exchange_open_, "exchange buffers are not open; call open_exchange first");
+      ex = exchange_desc();
+    }
+    LPLB_CUDA(lplb::launch_fused(idx.data_ptr(), is64, idx.numel(), topo(), ex, prm_, workspace_.data_ptr(),
+                                 probs_.data_ptr<float>(), avail.data_ptr(), avail.scalar_type() == torch::kInt64,
+                                 status_.data_ptr<int>(), out.data_ptr(), n_cta, grid_timeout_ns_, stream()));
+    return out;
+  }
+
+  // ---- exchange bootstrap ---------------------------------------------------------------
+  // Step 1 (every rank): allocate and return the IPC handle as bytes.
+  py::bytes alloc_exchange(int n_ranks, int my_rank) {
+    LPLB_CHECK(!block_.base, "exchange buffers already allocated");
+    LPLB_CHECK(n_ranks >= 2 && n_ranks <= 32 && my_rank >= 0 && my_rank < n_ranks, "bad rank layout");
+    c10::cuda::CUDAGuard guard(device_);
+    n_ranks_ = n_ranks;
+    my_rank_ = my_rank;
+    recv_bytes_ = sizeof(int) * 2 * (size_t)n_ranks * e_;
+    recv_bytes_ = (recv_bytes_ + 255) / 256 * 256;
+    block_.bytes = recv_bytes_ + 256;
+    LPLB_CUDA(cudaMalloc(&block_.base, block_.bytes));
+    LPLB_CUDA(cudaMemset(block_.base, 0, block_.bytes));
+    LPLB_CUDA(cudaDeviceSynchronize());
+    cudaIpcMemHandle_t handle;
+    LPLB_CUDA(cudaIpcGetMemHandle(&handle, block_.base));
+    return py::bytes(reinterpret_cast<const char*>(&handle), sizeof(handle));
+  }
+
+  // Step 2 (every rank, after the handles were all-gathered): map the peers.
+  void open_exchange(const std::vector<std::string>& handles) {
+    LPLB_CHECK(block_.base, "call alloc_exchange first");
+    LPLB_CHECK((int)handles.size() == n_ranks_, "need one handle per rank");
+    c10::cuda::CUDAGuard guard(device_);
+    std::vector<int64_t> recv(n_ranks_), flags(n_ranks_);
+    peers_.assign(n_ranks_, nullptr);
+    for (int r = 0; r < n_ranks_; ++r) {
+      void* base = block_.base;
+      if (r != my_rank_) {
+        LPLB_CHECK(handles[r].size() == sizeof(cudaIpcMemHandle_t), "malformed IPC handle from rank " << r);
+        cudaIpcMemHandle_t handle;
+        memcpy(&handle, handles[r].data(), sizeof(handle));
+        LPLB_CUDA(cudaIpcOpenMemHandle(&base, handle, cudaIpcMemLazyEnablePeerAccess));
+        peers_[r] = base;
+      }
+      recv[r] = reinterpret_cast<int64_t>(base);
+      flags[r] = reinterpret_cast<int64_t>(static_cast<char*>(base) + recv_bytes_);
+    }
+    auto opts = torch::TensorOptions().dtype(torch::kInt64);
+    recv_table_ = torch::from_blob(recv.data(), {n_ranks_}, opts).clone().to(torch::Device(torch::kCUDA, device_));
+    flag_table_ = torch::from_blob(flags.data(), {n_ranks_}, opts).clone().to(torch::Device(torch::kCUDA, device_));
+    exchange_open_ = true;
+  }
+
+  // Collective by convention: every rank calls it between steps, with no launch in flight,
+  // after a barrier.  Zeroes this rank's epochs, flags and receive buffers.
+  void reset_exchange() {
+    c10::cuda::CUDAGuard guard(device_);
+    LPLB_CUDA(cudaDeviceSynchronize());
+    workspace_.zero_();
+    if (block_.base) LPLB_CUDA(cudaMemset(block_.base, 0, block_.bytes));
+    LPLB_CUDA(cudaDeviceSynchronize());
+  }
+
+  void close_exchange() {
+    if (!block_.base) return;
+    c10::cuda::CUDAGuard guard(device_);
+    cudaDeviceSynchronize();
+    for (void* p : peers_)
+      if (p) cudaIpcCloseMemHandle(p);
+    peers_.clear();
+    cudaFree(block_.base);
+    block_.base = nullptr;
+    exchange_open_ = false;
+  }
+
+  bool exchange_open() const { return exchange_open_; }
+  torch::Tensor status() const { return status_; }
+  torch::Tensor last_probs() const { return probs_; }
+  torch::Tensor workspace() const { return workspace_; }
+  int n_logical() const { return e_; }
+  int max_fused_ctas(bool is64) {
+    c10::cuda::CUDAGuard guard(device_);
+    return lplb::max_fused_ctas(g_, d_, e_, is64);
+  }
+
+ private:
+  cudaStream_t stream() const { return c10::cuda::getCurrentCUDAStream(device_).stream(); }
+
+  torch::Tensor to_dev_i32(const torch::Tensor& t) const {
+    return t.to(torch::Device(torch::kCUDA, device_), torch::kInt32).contiguous().clone();
+  }
+
+  lplb::ExchangeDesc exchange_desc() const {
+    return lplb::ExchangeDesc{reinterpret_cast<int* const*>(recv_table_.data_ptr()),
+                              reinterpret_cast<uint32_t* const*>(flag_table_.data_ptr()), n_ranks_, my_rank_,
+                              peer_timeout_ns_};
+  }
+
+  void require_mapping() const {
+    LPLB_CHECK(r2o_.defined() && phy2log_.defined(), "topology and mapping must be set before launching");
+  }
+
+  void check_idx(const torch::Tensor& idx) const {
+    LPLB_CHECK(idx.is_cuda() && idx.get_device() == device_, "indices must live on cuda:" << device_);
+    LPLB_CHECK(idx.scalar_type() == torch::kInt64 || idx.scalar_type() == torch::kInt32, "indices must be int64 or int32");
+    LPLB_CHECK(idx.is_contiguous(), "indices must be contiguous");
+  }
+
+  void check_avail(const torch::Tensor& avail) const {
+    LPLB_CHECK(avail.is_cuda() && avail.numel() == 1 &&
+                   (avail.scalar_type() == torch::kInt32 || avail.scalar_type() == torch::kInt64),
+               "avail_counter must be a one-element int32 or int64 CUDA tensor");
+  }
+
+  lplb::TopoDesc topo() const {
+    return lplb::TopoDesc{r2o_.data_ptr<int>(),     o2r_.data_ptr<int>(),      phy2log_.data_ptr<int>(),
+                          log2phy_.data_ptr<int>(), log2edge_.data_ptr<int>(), n_group_, g_, d_, ll_, c_};
+  }
+
+  int n_group_, g_, d_, ll_, c_, e_, device_;
+  lplb::SolveParams prm_{24, 1e-4};
+  unsigned long long peer_timeout_ns_ = 1000000000ull, grid_timeout_ns_ = 1000000000ull;
+  torch::Tensor r2o_, o2r_, phy2log_, log2phy_, log2edge_;
+  torch::Tensor workspace_, status_, probs_;
+  int max_cta64_ = -1, max_cta32_ = -1;
+  // exchange
+  IpcBlock block_;
+  size_t recv_bytes_ = 0;
+  std::vector<void*> peers_;
+  torch::Tensor recv_table_, flag_table_;
+  int n_ranks_ = 1, my_rank_ = 0;
+  bool exchange_open_ = false;
+};
+
+}  // namespace
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  m.doc() = "lplb_b200 native runtime (sm_100a)";
+  py::class_<PlannerEngine>(m, "PlannerEngine")
+      .def(py::init<int, int, int, int, int, int>(), py::arg("n_group"), py::arg("group_size"),
+           py::arg("dup_per_rank"), py::arg("n_local_logical"), py::arg("n_combined"), py::arg("device"))
+      .def("set_topology", &PlannerEngine::set_topology)
+      .def("set_mapping", &PlannerEngine::set_mapping)
+      .def("set_params", &PlannerEngine::set_params)
+      .def("count_idx", &PlannerEngine::count_idx)
+      .def("solve", &PlannerEngine::solve)
+      .def("map_idx", &PlannerEngine::map_idx)
+      .def("run_fused", &PlannerEngine::run_fused)
+      .def("all_reduce_counts", &PlannerEngine::all_reduce_counts)
+      .def("alloc_exchange", &PlannerEngine::alloc_exchange)
+      .def("open_exchange", &PlannerEngine::open_exchange)
+      .def("reset_exchange", &PlannerEngine::reset_exchange)
+      .def("close_exchange", &PlannerEngine::close_exchange)
+      .def("exchange_open", &PlannerEngine::exchange_open)
+      .def("status", &PlannerEngine::status)
+      .def("last_probs", &PlannerEngine::last_probs)
+      .def("workspace", &PlannerEngine::workspace)
+      .def("n_logical", &PlannerEngine::n_logical)
+      .def("max_fused_ctas", &PlannerEngine::max_fused_ctas);
+  m.attr("MAX_GROUP_SIZE") = lplb::kMaxGroupSize;
+  m.attr("MAX_DUP") = lplb::kMaxDup;
+  m.attr("MAX_LOGICAL_EXPERTS") = lplb::kMaxLogicalExperts;
+}

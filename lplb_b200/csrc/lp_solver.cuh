@@ -1,0 +1,342 @@
+// Warp-level interior-point solver for the per-group balancing LP (sm_100a).
+//
+//   min t  s.t.  base_i + sum_k M[i,k] f_k <= t,  0 <= f <= 1
+//
+// One LP group of G <= GP ranks is solved by GP consecutive lanes of a warp; a warp
+// therefore carries 32/GP independent groups at once.  Lane i is rank i and owns the D
+// edges (i, d): the replicated bundles whose origin is rank i.  All cross-rank traffic
+// is warp shuffles with segment width GP, nothing goes through shared memory and there
+// is no block barrier inside the iteration.
+//
+// The method is a Mehrotra predictor-corrector primal-dual iteration in float64 on the
+// compact form.  The normal matrix N = M diag(theta) M^T + diag(s/y) is a weighted
+// graph Laplacian of the topology plus a positive diagonal, GP x GP.  Lane i keeps row i
+// in registers; the Cholesky factorisation updates both triangles so that after step j
+// lane j already holds column j of L, which lets forward and backward substitution run
+// with statically indexed registers.
+//
+// It replaces the reference's primal affine-scaling loop on the (G+GD) x (2GD+G+2)
+// equality form with cuBLASDx/cuSolverDx block calls
+// (reference lplb/resources/csrc-tmpl/minilp.cu:28-59 and :323-401): a 24x24 system
+// shrinks to 8x8 for the Cube, 96x96 to 32x32 for the 8x4 torus, the start point is
+// feasible without a big-M column, and the loop stops on a duality-gap test instead of
+// after a fixed five steps.
+#pragma once
+
+#ifdef LPLB_HOST_SIM
+#include "host_sim.h"
+#else
+#include <cuda_runtime.h>
+#endif
+#include <math.h>
+
+namespace lplb {
+
+struct IpmParams {
+  int max_iters;   // hard cap on iterations
+  double tol;      // relative duality gap and feasibility target
+};
+
+struct IpmOutcome {
+  int iters;
+  bool converged;
+  bool finite;
+  double gap;
+};
+
+template <int GP>
+__device__ __forceinline__ double seg_shfl(double v, int src) {
+  return __shfl_sync(0xffffffffu, v, src, GP);
+}
+template <int GP>
+__device__ __forceinline__ double seg_sum(double v) {
+#pragma unroll
+  for (int o = GP / 2; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o, GP);
+  return v;
+}
+template <int GP>
+__device__ __forceinline__ double seg_max(double v) {
+#pragma unroll
+  for (int o = GP / 2; o > 0; o >>= 1) v = fmax(v, __shfl_xor_sync(0xffffffffu, v, o, GP));
+  return v;
+}
+template <int GP>
+__device__ __forceinline__ float seg_minf(float v) {
+#pragma unroll
+  for (int o = GP / 2; o > 0; o >>= 1) v = fminf(v, __shfl_xor_sync(0xffffffffu, v, o, GP));
+  return v;
+}
+
+// Largest step in [0, +inf) that keeps val + a*dval >= 0, as a float (the 0.995 safety
+// fraction applied by the caller dwarfs the rounding of this ratio).
+__device__ __forceinline__ float ratio_to_bound(double val, double dval) {
+  return dval < 0.0 ? __fdividef((float)val, -(float)dval) : 3.0e38f;
+}
+
+// Solve L L^T x = g for two right-hand sides held one element per lane.  `row` is the
+// factor as left by the factorisation in ipm_solve_segment: on lane i, row[j<i] = L[i][j],
+// row[i] = 1/L[i][i], row[j>i] = L[j][i].
+template <int GP>
+__device__ __forceinline__ void chol_solve2(const double (&row)[GP], int li, double& g0, double& g1) {
+#pragma unroll
+  for (int j = 0; j < GP; ++j) {
+    const double x0 = seg_shfl<GP>(g0 * row[j], j), x1 = seg_shfl<GP>(g1 * row[j], j);
+    if (li > j) {
+      g0 -= row[j] * x0;
+      g1 -= row[j] * x1;
+    } else if (li == j) {
+      g0 = x0;
+      g1 = x1;
+    }
+  }
+#pragma unroll
+  for (int j = GP - 1; j >= 0; --j) {
+    const double x0 = seg_shfl<GP>(g0 * row[j], j), x1 = seg_shfl<GP>(g1 * row[j], j);
+    if (li < j) {
+      g0 -= row[j] * x0;
+      g1 -= row[j] * x1;
+    } else if (li == j) {
+      g0 = x0;
+      g1 = x1;
+    }
+  }
+}
+
+// All 32 lanes must call this together.  `li` is the lane's index inside its segment.
+//   w[d]      load of own bundle d (any non-negative unit)
+//   fixed     load of the lane's non-replicated experts (same unit)
+//   src[d]    segment lane whose bundle d this rank holds a replica of  (r2o[i][d])
+//   dst[d]    segment lane that holds the replica of own bundle d       (o2r[i][d])
+// Padding lanes (rank >= G) pass w = 0, fixed = 0, src = dst = li.
+// Returns the shares f[d] of own bundles kept on the origin, clamped to [0, 1].
+template <int GP, int D>
+__device__ IpmOutcome ipm_solve_segment(int li, const double (&w_in)[D], double fixed, const int (&src)[D],
+                                        const int (&dst)[D], const IpmParams prm, double (&f_out)[D]) {
+  constexpr double kEta = 0.995;
+  constexpr int kComp = GP + 2 * GP * D;
+
+  // ---- scale so that the mean rank load is 1 ---------------------------------------
+  double mine = fixed;
+#pragma unroll
+  for (int d = 0; d < D; ++d) mine += w_in[d];
+  const double total = seg_sum<GP>(mine);
+  IpmOutcome out{0, true, true, 0.0};
+  // A segment with no load at all (also: a segment past the last group) must still walk
+  // through every shuffle below with the rest of the warp, so it is not returned early:
+  // it starts out `done`, computes on harmless zeros and reports f = 1 at the end.
+  const bool empty = !(total > 0.0);
+  const double inv_scale = empty ? 0.0 : (double)GP / total;
+  double w[D], base = fixed * inv_scale;
+#pragma unroll
+  for (int d = 0; d < D; ++d) {
+    w[d] = w_in[d] * inv_scale;
+    base += seg_shfl<GP>(w[d], src[d]);
+  }
+  // A self edge (origin == holder; also every padding lane) moves no load: its column
+  // of M is zero.  Its load is already part of `base`, so drop the weight.
+#pragma unroll
+  for (int d = 0; d < D; ++d)
+    if (dst[d] == li) w[d] = 0.0;
+
+  auto m_times = [&](const double(&x)[D]) -> double {  // (M x)_i
+    double acc = 0.0;
+#pragma unroll
+    for (int d = 0; d < D; ++d) {
+      const double wx = w[d] * x[d];
+      acc += wx - seg_shfl<GP>(wx, src[d]);
+    }
+    return acc;
+  };
+
+  // ---- feasible start ------------------------------------------------------------------
+  double f[D], v[D], z[D], q[D];
+#pragma unroll
+  for (int d = 0; d < D; ++d) f[d] = v[d] = 0.5;
+  double load = base + m_times(f);
+  const double lmax = seg_max<GP>(load), lmin = -seg_max<GP>(-load);
+  double t = lmax + 0.5 * (lmax - lmin) + 0.05;
+  double s = t - load;
+  double y = 1.0 / GP;
+  {
+    const double mu0 = seg_sum<GP>(s * y) / GP;
+#pragma unroll
+    for (int d = 0; d < D; ++d) z[d] = q[d] = 2.0 * mu0;
+  }
+
+  bool done = empty;
+  int iters = 0;
+  double gap = 1e300;
+
+  for (int it = 0; it <= prm.max_iters; ++it) {
+    // ---- residuals, gap, stopping test ---------------------------------------------
+    const double mf = m_times(f);
+    const double r_p = t - base - mf - s;
+    double r_u[D], r_d[D];
+    double comp = s * y, dual_part = y * base, neg_rd = 0.0, worst_u = 0.0;
+#pragma unroll
+    for (int d = 0; d < D; ++d) {
+      r_u[d] = 1.0 - f[d] - v[d];
+      r_d[d] = z[d] - q[d] - w[d] * (y - seg_shfl<GP>(y, dst[d]));
+      comp += z[d] * f[d] + q[d] * v[d];
+      dual_part -= q[d];
+      neg_rd += fmin(r_d[d], 0.0);
+      worst_u = fmax(worst_u, fabs(r_u[d]));
+    }
+    const double mu = seg_sum<GP>(comp) / kComp;
+    const double r_t = 1.0 - seg_sum<GP>(y);
+    const double primal = seg_max<GP>(base + mf);
+    const double dual = seg_sum<GP>(dual_part + neg_rd);
+    const double infeas = fmax(seg_max<GP>(worst_u), fabs(r_t));
+    if (!done) {
+      gap = (primal - dual) / fmax(fabs(primal), 1e-300);
+      if (gap <= prm.tol && infeas <= prm.tol) done = true;
+    }
+    // Every segment of the warp has to leave the loop together.
+    if (__all_sync(0xffffffffu, done) || it == prm.max_iters) break;
+    if (!done) ++iters;
+
+    // ---- normal matrix row -----------------------------------------------------------
+    double inv_f[D], inv_v[D], theta[D], cw[D];
+    const double inv_y = 1.0 / y;
+#pragma unroll
+    for (int d = 0; d < D; ++d) {
+      inv_f[d] = 1.0 / f[d];
+      inv_v[d] = 1.0 / v[d];
+      theta[d] = 1.0 / (z[d] * inv_f[d] + q[d] * inv_v[d]);
+      cw[d] = theta[d] * w[d] * w[d];
+    }
+    double row[GP];
+    {
+      double diag = s * inv_y;
+      double held[D];
+#pragma unroll
+      for (int d = 0; d < D; ++d) {
+        held[d] = seg_shfl<GP>(cw[d], src[d]);
+        diag += cw[d] + held[d];
+      }
+#pragma unroll
+      for (int j = 0; j < GP; ++j) {
+        double e = (j == li) ? diag : 0.0;
+#pragma unroll
+        for (int d = 0; d < D; ++d) {
+          e -= (dst[d] == j) ? cw[d] : 0.0;
+          e -= (src[d] == j) ? held[d] : 0.0;
+        }
+        row[j] = e;
+      }
+    }
+
+    // ---- Cholesky, both triangles kept current -------------------------------------------
+    // afterwards on lane i: row[j<i] = L[i][j], row[i] = 1/L[i][i], row[j>i] = L[j][i]
+#pragma unroll
+    for (int j = 0; j < GP; ++j) {
+      double piv = seg_shfl<GP>(row[j], j);
+      if (!(piv > 1e-300) || !(piv < 1e300)) piv = 1e300;  // drop a dead pivot instead of emitting NaN
+      const double rinv = rsqrt(piv);
+      if (li == j) {
+#pragma unroll
+        for (int k = j + 1; k < GP; ++k) row[k] *= rinv;
+        row[j] = rinv;
+      }
+      const double lij = row[j] * rinv;  // meaningful on lanes > j
+#pragma unroll
+      for (int k = j + 1; k < GP; ++k) {
+        const double lk = seg_shfl<GP>(row[k], j);
+        if (li > j) row[k] -= lij * lk;
+      }
+      if (li > j) row[j] = lij;
+    }
+
+    // ---- predictor (pass 0) and corrector (pass 1) share one body ------------------------
+    // Pass 0 also solves N b = 1 for the border column that carries sum(dy) = r_t; pass 1
+    // sends a dummy second right-hand side through the same substitution code.
+    double df[D], dv[D], dz[D], dq[D], ds = 0.0, dy = 0.0, dt = 0.0;
+    double border = 1.0, border_sum = 1.0, sm = 0.0;
+#pragma unroll
+    for (int d = 0; d < D; ++d) df[d] = dv[d] = dz[d] = dq[d] = 0.0;
+    float apf = 0.f, adf = 0.f;
+#pragma unroll 1
+    for (int pass = 0; pass < 2; ++pass) {
+      // complementarity targets: -XZe for the predictor, sigma*mu*e - XZe - dXdZe after it
+      const double r_sy = sm - s * y - ds * dy;
+      double r_zf[D], r_qv[D], rd_t[D];
+      double acc = 0.0;
+#pragma unroll
+      for (int d = 0; d < D; ++d) {
+        r_zf[d] = sm - z[d] * f[d] - dz[d] * df[d];
+        r_qv[d] = sm - q[d] * v[d] - dq[d] * dv[d];
+        rd_t[d] = r_d[d] + r_zf[d] * inv_f[d] - (r_qv[d] - q[d] * r_u[d]) * inv_v[d];
+        const double wx = w[d] * theta[d] * rd_t[d];
+        acc += wx - seg_shfl<GP>(wx, src[d]);
+      }
+      double a = acc - r_p + r_sy * inv_y;
+      double b2 = pass == 0 ? 1.0 : 0.0;
+      chol_solve2<GP>(row, li, a, b2);
+      if (pass == 0) {
+        border = b2;
+        border_sum = seg_sum<GP>(border);
+      }
+      dt = (seg_sum<GP>(a) - r_t) / border_sum;
+      dy = a - dt * border;
+      ds = (r_sy - s * dy) * inv_y;
+      float rp = ratio_to_bound(s, ds), rd = ratio_to_bound(y, dy);
+#pragma unroll
+      for (int d = 0; d < D; ++d) {
+        df[d] = theta[d] * (rd_t[d] - w[d] * (dy - seg_shfl<GP>(dy, dst[d])));
+        dv[d] = r_u[d] - df[d];
+        dz[d] = (r_zf[d] - z[d] * df[d]) * inv_f[d];
+        dq[d] = (r_qv[d] - q[d] * dv[d]) * inv_v[d];
+        rp = fminf(rp, fminf(ratio_to_bound(f[d], df[d]), ratio_to_bound(v[d], dv[d])));
+        rd = fminf(rd, fminf(ratio_to_bound(z[d], dz[d]), ratio_to_bound(q[d], dq[d])));
+      }
+      apf = seg_minf<GP>(rp);
+      adf = seg_minf<GP>(rd);
+      if (pass == 0) {  // centring parameter from the affine step
+        const double ap = fmin((double)apf, 1.0), ad = fmin((double)adf, 1.0);
+        double comp_aff = (s + ap * ds) * (y + ad * dy);
+#pragma unroll
+        for (int d = 0; d < D; ++d)
+          comp_aff += (z[d] + ad * dz[d]) * (f[d] + ap * df[d]) + (q[d] + ad * dq[d]) * (v[d] + ap * dv[d]);
+        const double ratio = fmin(fmax(seg_sum<GP>(comp_aff) / (kComp * mu), 0.0), 1.0);
+        sm = ratio * ratio * ratio * mu;
+      }
+    }
+    const double ap = fmin(kEta * (double)apf, 1.0), ad = fmin(kEta * (double)adf, 1.0);
+    if (!done) {
+      t += ap * dt;
+      s += ap * ds;
+      y += ad * dy;
+#pragma unroll
+      for (int d = 0; d < D; ++d) {
+        f[d] += ap * df[d];
+        v[d] += ap * dv[d];
+        z[d] += ad * dz[d];
+        q[d] += ad * dq[d];
+      }
+    }
+  }
+
+  bool finite = true;
+#pragma unroll
+  for (int d = 0; d < D; ++d) {
+    finite = finite && (f[d] == f[d]) && fabs(f[d]) < 1e300;
+    f_out[d] = fmin(fmax(f[d], 0.0), 1.0);
+  }
+  finite = seg_max<GP>(finite ? 0.0 : 1.0) == 0.0;
+  if (!finite) {
+#pragma unroll
+    for (int d = 0; d < D; ++d) f_out[d] = 0.5;
+  }
+  if (empty) {  // nothing to balance: keep everything on the origin
+#pragma unroll
+    for (int d = 0; d < D; ++d) f_out[d] = 1.0;
+    gap = 0.0;
+  }
+  out.iters = iters;
+  out.converged = done && finite;
+  out.finite = finite;
+  out.gap = gap;
+  return out;
+}
+
+}  // namespace lplb

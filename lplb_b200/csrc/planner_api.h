@@ -1,0 +1,70 @@
+// Host-side launch interface of the planner kernels.  Plain C++ with raw device pointers
+// and a stream so that the CUDA translation units do not need the torch headers; the
+// pybind layer (binding.cpp) owns tensors, shapes and allocation.
+//
+// Counterpart of the launchers in the reference's csrc/plugin.cpp:491-660.  There is no
+// run-time compiler here: every (group size, replicas per rank) shape is instantiated
+// ahead of time for sm_100a, which removes the NVRTC/nvJitLink/disk-cache machinery of
+// reference csrc/plugin.cpp:149-352.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+namespace lplb {
+
+struct TopoDesc {
+  const int* r2o;
+  const int* o2r;
+  const int* phy2log;
+  const int* log2phy;
+  const int* log2edge;
+  int n_group, g, d, ll, c;
+};
+
+struct ExchangeDesc {
+  int* const* recv;          // device array of n_ranks pointers (nullptr when n_ranks == 1)
+  uint32_t* const* flags;    // device array of n_ranks pointers
+  int n_ranks;
+  int my_rank;
+  unsigned long long timeout_ns;
+};
+
+struct SolveParams {
+  int max_iters;
+  double tol;
+};
+
+// Largest group size / replicas per rank that the warp solver is instantiated for.
+constexpr int kMaxGroupSize = 32;
+constexpr int kMaxDup = 4;
+constexpr int kMaxLogicalExperts = 8192;
+
+size_t planner_workspace_bytes(int n_logical);
+
+// idx_is64: 1 for int64 indices, 0 for int32.  All functions return a cudaError_t from the
+// launch (cudaSuccess when enqueued); cudaErrorInvalidValue for unsupported shapes.
+cudaError_t launch_count(const void* idx, int idx_is64, long long n, int n_logical, int n_cta, int* by_cta,
+                         void* workspace, int* status, cudaStream_t stream);
+
+cudaError_t launch_solve(const int* workload, const TopoDesc& topo, SolveParams prm, float* probs, float* normalised,
+                         void* avail, int avail_is64, int* status, cudaStream_t stream);
+
+cudaError_t launch_redirect(const void* idx, int idx_is64, long long n, const float* probs, const int* by_cta,
+                            const TopoDesc& topo, int n_cta, void* out, cudaStream_t stream);
+
+// Sum int32[E] counts over the peers of `ex` (in-kernel push over NVLink peer memory).
+cudaError_t launch_exchange(const int* in, int n_logical, const ExchangeDesc& ex, void* workspace, int* out,
+                            int* status, cudaStream_t stream);
+
+// Single-launch count + exchange + solve + redirect.  Cooperative launch: n_cta must not
+// exceed max_fused_ctas().
+cudaError_t launch_fused(const void* idx, int idx_is64, long long n, const TopoDesc& topo, const ExchangeDesc& ex,
+                         SolveParams prm, void* workspace, float* probs, void* avail, int avail_is64, int* status,
+                         void* out, int n_cta, unsigned long long grid_timeout_ns, cudaStream_t stream);
+
+// Co-resident CTA limit of the fused kernel for this shape on the current device.
+int max_fused_ctas(int g, int d, int n_logical, int idx_is64);
+
+}  // namespace lplb

@@ -1,0 +1,439 @@
+// Planner kernels for sm_100a: token histogram, statistics exchange over NVLink peer
+// memory, per-group LP solve, index redirect, and the single-launch fusion of all four.
+//
+// Reference counterparts (lplb/resources/csrc-tmpl/minilp.cu): kernel_count_idx :410-443,
+// the communication phase of kernel_solve :109-197, its LP phase :199-401 and
+// kernel_map_idx :445-515.  None of the code below is derived from them; the contracts
+// that are kept are the tensor shapes of the Python API.
+#pragma once
+
+#include "common.cuh"
+#include "lp_solver.cuh"
+
+namespace lplb {
+
+constexpr int kBlock = 256;          // threads per CTA for every planner kernel
+constexpr int kWarps = kBlock / 32;
+constexpr int kMaxExperts = 8192;    // logical experts supported by the shared-memory tables
+
+// Static description of one placement (device pointers, uploaded once per mapping).
+struct Topo {
+  const int* r2o;       // [G, D]   source rank of replica slot d
+  const int* o2r;       // [G, D]   holder rank of own bundle d
+  const int* phy2log;   // [NG*G*Pl]
+  const int* log2phy;   // [E, 2]   (original, replica or -1)
+  const int* log2edge;  // [E]      index into probs[NG*G*D] or -1
+  int n_group, g, d, ll, c, pl, e;
+};
+
+// Peer-memory exchange state.  recv[r] points at rank r's receive buffer
+// int32[2][n_ranks][E] (two epochs' worth), flags[r] at rank r's uint32[n_ranks].
+struct Exchange {
+  int* const* recv;
+  uint32_t* const* flags;
+  int n_ranks;
+  int my_rank;
+  unsigned long long timeout_ns;
+};
+
+// Per-engine scratch in this GPU's memory; zero-initialised by the host once.
+struct Workspace {
+  uint32_t epoch;     // launches completed
+  uint32_t arrive;    // CTAs of the running launch that published their counts
+  uint32_t lp_done;   // epoch whose shares are ready
+  uint32_t exit_cnt;  // CTAs of the running launch that finished
+  uint32_t count_ticket;  // used by the stand-alone counting kernel
+  uint32_t pad[3];
+  // followed by: int total[2][E]; int global_cnt[E];
+};
+__host__ __device__ inline size_t workspace_bytes(int e) { return sizeof(Workspace) + sizeof(int) * 3 * (size_t)e; }
+__device__ __forceinline__ int* ws_total(Workspace* ws, int parity, int e) {
+  return reinterpret_cast<int*>(ws + 1) + (size_t)parity * e;
+}
+__device__ __forceinline__ int* ws_global(Workspace* ws, int e) { return reinterpret_cast<int*>(ws + 1) + 2 * (size_t)e; }
+
+// ---------------------------------------------------------------------------------------
+// Histogram of one CTA's token slice into shared memory.  Indices outside [-1, E) are
+// ignored and counted in the status block.
+template <typename IdxT>
+__device__ __forceinline__ void histogram_slice(const IdxT* __restrict__ idx, long long begin, long long end, int e,
+                                                int* __restrict__ hist, int* status) {
+  int bad = 0;
+  for (long long i = begin + threadIdx.x; i < end; i += kBlock) {
+    const long long v = (long long)idx[i];
+    if (v >= 0 && v < e) atomicAdd(&hist[v], 1);
+    else if (v != -1) ++bad;
+  }
+  if (bad) {
+    atomicAdd(&status[kStBadIdx], bad);
+    raise_status(status, kErrBadIndex, kPhCount, bad);
+  }
+}
+
+// Spread `quota` picks evenly over `total` ordinals: ordinal k is a pick iff
+// floor((k+1)*quota/total) > floor(k*quota/total), i.e. (k*quota mod total) + quota >= total.
+// Exactly `quota` of the ordinals 0..total-1 are picks for any 0 <= quota <= total, which
+// the reference's multiplicative hash only guarantees when 499 does not divide total
+// (reference minilp.cu:505).
+__device__ __forceinline__ bool even_pick(unsigned k, unsigned quota, unsigned total) {
+  if (quota >= total) return true;
+  if (quota == 0) return false;
+  unsigned rem;
+  if (total <= 65536u) rem = (k * quota) % total;  // k < total, quota < total: fits in 32 bits
+  else rem = (unsigned)(((unsigned long long)k * quota) % total);
+  return rem + quota >= total;
+}
+
+// Quota of expert e's local tokens that stay on the original.
+__device__ __forceinline__ int quota_of(int total, int edge, const float* __restrict__ probs) {
+  if (edge < 0) return total;
+  float p = __ldcg(&probs[edge]);  // may have been written by another CTA of this launch
+  p = p != p ? 0.5f : fminf(fmaxf(p, 0.f), 1.f);
+  int q = __float2int_rn(p * (float)total);
+  return q < 0 ? 0 : (q > total ? total : q);
+}
+
+template <typename IdxT>
+__device__ __forceinline__ void redirect_slice(const IdxT* __restrict__ idx, long long begin, long long end, int e,
+                                               int* __restrict__ cur, const int* __restrict__ total,
+                                               const int* __restrict__ quota, const int2* __restrict__ phys,
+                                               IdxT* __restrict__ out) {
+  for (long long i = begin + threadIdx.x; i < end; i += kBlock) {
+    const long long v = (long long)idx[i];
+    long long o = -1;
+    if (v >= 0 && v < e) {
+      const int2 ph = phys[v];
+      const int k = atomicAdd(&cur[v], 1);
+      const bool keep = ph.y < 0 || even_pick((unsigned)k, (unsigned)quota[v], (unsigned)total[v]);
+      o = keep ? ph.x : ph.y;
+    }
+    out[i] = (IdxT)o;
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// Stand-alone counting kernel.  Row p of `by_cta` receives CTA p's counts; the CTA that
+// finishes last turns the rows into inclusive prefixes over CTAs, so row n_cta-1 is the
+// rank-local total.  No cooperative launch and no spinning: the last arriver is found
+// with a ticket.
+template <typename IdxT>
+__global__ void __launch_bounds__(kBlock) count_kernel(const IdxT* __restrict__ idx, long long n, int e,
+                                                       int* __restrict__ by_cta, Workspace* ws, int* status) {
+  extern __shared__ int smem[];
+  int* hist = smem;
+  __shared__ bool last;
+  const int p = blockIdx.x, n_cta = gridDim.x;
+  for (int i = threadIdx.x; i < e; i += kBlock) hist[i] = 0;
+  __syncthreads();
+  histogram_slice(idx, slice_begin(n, p, n_cta, kBlock), slice_begin(n, p + 1, n_cta, kBlock), e, hist, status);
+  __syncthreads();
+  for (int i = threadIdx.x; i < e; i += kBlock) by_cta[(size_t)p * e + i] = hist[i];
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) last = atomicAdd(&ws->count_ticket, 1u) == (unsigned)n_cta - 1;
+  __syncthreads();
+  if (!last) return;
+  __threadfence();
+  for (int i = threadIdx.x; i < e; i += kBlock) {
+    int run = 0;
+    for (int r = 0; r < n_cta; ++r) {
+      run += __ldcg(&by_cta[(size_t)r * e + i]);
+      by_cta[(size_t)r * e + i] = run;
+    }
+  }
+  if (threadIdx.x == 0) ws->count_ticket = 0;
+}
+
+// ---------------------------------------------------------------------------------------
+// LP phase shared by the stand-alone solve kernel and the fused kernel.  `cnt` holds the
+// group-wide (already summed over ranks) counts per logical expert, in shared or global
+// memory.  Each warp carries 32/GP groups; a CTA covers `kWarps * 32/GP` groups per round.
+// The success counter may be an int32 or an int64 tensor (the reference's README shows
+// int64, its launcher demands int32: reference README.md:32, csrc/plugin.cpp:528-529).
+struct Counter {
+  void* ptr;
+  int is64;
+};
+__device__ __forceinline__ void bump(Counter c) {
+  if (c.is64) atomicAdd(reinterpret_cast<unsigned long long*>(c.ptr), 1ull);
+  else atomicAdd(reinterpret_cast<int*>(c.ptr), 1);
+}
+
+template <int GP, int D>
+__device__ void solve_groups(const int* __restrict__ cnt, const Topo& tp, int first_group, int group_stride,
+                             IpmParams prm, float* __restrict__ probs, Counter avail, int* status) {
+  constexpr int kSeg = 32 / GP;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int seg = lane / GP, li = lane % GP;
+  for (int g0 = first_group + warp * kSeg; g0 < tp.n_group; g0 += group_stride) {
+    const int grp = g0 + seg;
+    const bool live = grp < tp.n_group && li < tp.g;
+    double w[D], fixed = 0.0, f[D];
+    int src[D], dst[D];
+#pragma unroll
+    for (int d = 0; d < D; ++d) {
+      w[d] = 0.0;
+      src[d] = dst[d] = li;
+    }
+    if (live) {
+      const int* slots = tp.phy2log + ((size_t)grp * tp.g + li) * tp.pl;
+      const int n_rep = tp.c * D;
+      for (int sl = 0; sl < n_rep; ++sl) {
+        const double x = (double)cnt[slots[sl]];
+#pragma unroll
+        for (int d = 0; d < D; ++d)
+          if (sl % D == d) w[d] += x;
+      }
+      for (int sl = n_rep; sl < tp.ll; ++sl) fixed += (double)cnt[slots[sl]];
+#pragma unroll
+      for (int d = 0; d < D; ++d) {
+        src[d] = tp.r2o[li * D + d];
+        dst[d] = tp.o2r[li * D + d];
+      }
+    }
+    const IpmOutcome res = ipm_solve_segment<GP, D>(li, w, fixed, src, dst, prm, f);
+    if (live) {
+#pragma unroll
+      for (int d = 0; d < D; ++d) probs[((size_t)grp * tp.g + li) * D + d] = (float)f[d];
+      if (li == 0) {
+        if (res.converged) bump(avail);
+        else {
+          atomicAdd(&status[kStLpFail], 1);
+          raise_status(status, kErrLpNotConverged, kPhSolve, grp);
+        }
+        atomicMax(&status[kStLpIters], res.iters);
+      }
+    }
+  }
+}
+
+// Stand-alone solve kernel: one CTA per `kWarps * 32/GP` groups.  `workload` is int32[E],
+// already summed over ranks by the caller.  Also writes the counts divided by their
+// maximum, which the Python API returns next to the shares
+// (reference csrc/plugin.cpp:504-506, :577).
+template <int GP, int D>
+__global__ void __launch_bounds__(kBlock) solve_kernel(const int* __restrict__ workload, Topo tp, IpmParams prm,
+                                                       float* __restrict__ probs, float* __restrict__ normalised,
+                                                       Counter avail, int* status) {
+  __shared__ int wmax[kWarps];
+  if (blockIdx.x == 0) {
+    int m = 0;
+    for (int i = threadIdx.x; i < tp.e; i += kBlock) m = max(m, workload[i]);
+    for (int o = 16; o > 0; o >>= 1) m = max(m, __shfl_xor_sync(0xffffffffu, m, o));
+    if ((threadIdx.x & 31) == 0) wmax[threadIdx.x >> 5] = m;
+    __syncthreads();
+    m = 0;
+    for (int i = 0; i < kWarps; ++i) m = max(m, wmax[i]);
+    const float inv = m > 0 ? 1.f / (float)m : 0.f;
+    for (int i = threadIdx.x; i < tp.e; i += kBlock) normalised[i] = (float)workload[i] * inv;
+    if (threadIdx.x == 0) status[kStLpIters] = 0;
+    __syncthreads();
+  }
+  constexpr int kPerCta = kWarps * (32 / GP);
+  solve_groups<GP, D>(workload, tp, blockIdx.x * kPerCta, gridDim.x * kPerCta, prm, probs, avail, status);
+}
+
+// ---------------------------------------------------------------------------------------
+// Stand-alone redirect kernel.  Must run with the grid of the counting kernel that made
+// `by_cta` (the same coupling exists in the reference, minilp.cu:468-470 and :498-499).
+template <typename IdxT>
+__global__ void __launch_bounds__(kBlock) redirect_kernel(const IdxT* __restrict__ idx, long long n,
+                                                          const float* __restrict__ probs,
+                                                          const int* __restrict__ by_cta, Topo tp,
+                                                          IdxT* __restrict__ out) {
+  extern __shared__ int smem[];
+  const int e = tp.e, p = blockIdx.x, n_cta = gridDim.x;
+  int* total = smem;
+  int* cur = total + e;
+  int* quota = cur + e;
+  int2* phys = reinterpret_cast<int2*>(quota + e);
+  for (int i = threadIdx.x; i < e; i += kBlock) {
+    const int tot = by_cta[(size_t)(n_cta - 1) * e + i];
+    total[i] = tot;
+    cur[i] = p == 0 ? 0 : by_cta[(size_t)(p - 1) * e + i];
+    quota[i] = quota_of(tot, tp.log2edge[i], probs);
+    phys[i] = reinterpret_cast<const int2*>(tp.log2phy)[i];
+  }
+  __syncthreads();
+  redirect_slice(idx, slice_begin(n, p, n_cta, kBlock), slice_begin(n, p + 1, n_cta, kBlock), e, cur, total, quota,
+                 phys, out);
+}
+
+// ---------------------------------------------------------------------------------------
+// All-reduce of int32[E] counts over the ranks of one NVLink domain, called by one CTA.
+// Push model: every rank stores its vector into slot `my_rank` of every peer's receive
+// buffer (plain st over NVLink), then raises one flag per peer with a system-scope
+// release store; it then acquires one flag per peer and sums the slots in its own
+// memory.  Two receive buffers alternate by epoch parity: a rank can only be one launch
+// ahead of the slowest peer (it needs that peer's flag of the current epoch to finish),
+// so the buffer it overwrites is never still being read.  `mine` and `sum` are
+// shared-memory arrays of E ints.  Returns a bit mask of peers that never arrived.
+__device__ __forceinline__ unsigned exchange_counts(const Exchange& ex, uint32_t epoch, int e, const int* mine,
+                                                    int* sum) {
+  __shared__ unsigned missing;
+  const int parity = epoch & 1;
+  if (threadIdx.x == 0) missing = 0;
+  for (int r = 0; r < ex.n_ranks; ++r) {
+    int* slot = ex.recv[r] + ((size_t)parity * ex.n_ranks + ex.my_rank) * e;
+    for (int i = threadIdx.x; i < e; i += kBlock) slot[i] = mine[i];
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x < ex.n_ranks) {
+    st_release_sys(ex.flags[threadIdx.x] + ex.my_rank, epoch);
+    if (!bounded_wait_ge<true>(ex.flags[ex.my_rank] + threadIdx.x, epoch, ex.timeout_ns))
+      atomicOr(&missing, 1u << (threadIdx.x & 31));
+  }
+  __syncthreads();
+  const unsigned miss = missing;
+  const int* base = ex.recv[ex.my_rank] + (size_t)parity * ex.n_ranks * e;
+  for (int i = threadIdx.x; i < e; i += kBlock) {
+    int acc = 0;
+    for (int r = 0; r < ex.n_ranks; ++r) {
+      // a peer that never arrived contributes this rank's own counts instead of stale data
+      const bool absent = (miss >> (r & 31)) & 1u;
+      acc += absent ? mine[i] : __ldcv(&base[(size_t)r * e + i]);
+    }
+    sum[i] = acc;
+  }
+  __syncthreads();
+  return miss;
+}
+
+// ---------------------------------------------------------------------------------------
+// Stand-alone all-reduce of int32[E] counts over the peers (one CTA), for callers that
+// feed their own statistics to the solver.  Shares the epoch with the fused kernel, so it
+// keeps that kernel's invariant: the totals of the other parity are zero when it ends.
+__global__ void __launch_bounds__(kBlock) exchange_kernel(const int* __restrict__ in, int e, Exchange ex,
+                                                          Workspace* ws, int* __restrict__ out, int* status) {
+  extern __shared__ int smem[];
+  int* mine = smem;
+  int* summed = smem + e;
+  const uint32_t epoch = ld_acquire_gpu(&ws->epoch) + 1;
+  int* other = ws_total(ws, (epoch & 1) ^ 1, e);
+  for (int i = threadIdx.x; i < e; i += kBlock) {
+    mine[i] = in[i];
+    other[i] = 0;
+  }
+  __syncthreads();
+  const unsigned miss = exchange_counts(ex, epoch, e, mine, summed);
+  if (miss && threadIdx.x == 0) {
+    atomicAdd(&status[kStTimeouts], 1);
+    raise_status(status, kErrPeerTimeout, kPhExchange, (int)miss);
+  }
+  for (int i = threadIdx.x; i < e; i += kBlock) out[i] = summed[i];
+  __syncthreads();
+  if (threadIdx.x == 0) st_release_gpu(&ws->epoch, epoch);
+}
+
+// ---------------------------------------------------------------------------------------
+// Single-launch planner step.  Launched cooperatively so that all CTAs are co-resident.
+//
+//   every CTA : histogram its slice; reserve an ordinal range per expert with one
+//               returning atomicAdd on the rank-local totals; arrive.
+//   CTA 0     : wait for all arrivals; exchange totals with the peers; solve the LPs
+//               (one warp segment per group); publish the shares; raise lp_done.
+//   every CTA : wait for lp_done; turn shares into integer quotas; rewrite its slice.
+//
+// The ordinal ranges come from atomics, so which CTA gets which range differs from run
+// to run; quotas are exact regardless.  Shared memory: 5 int arrays of E entries.
+template <int GP, int D, typename IdxT>
+__global__ void __launch_bounds__(kBlock) fused_run_kernel(const IdxT* __restrict__ idx, long long n, Topo tp,
+                                                           Exchange ex, IpmParams prm, Workspace* ws,
+                                                           float* __restrict__ probs, Counter avail, int* status,
+                                                           IdxT* __restrict__ out, unsigned long long grid_timeout_ns) {
+  extern __shared__ int smem[];
+  const int e = tp.e, p = blockIdx.x, n_cta = gridDim.x;
+  int* hist = smem;        // this CTA's counts, later the rank-local totals
+  int* cur = hist + e;     // next ordinal to hand out per expert
+  int* quota = cur + e;
+  int2* phys = reinterpret_cast<int2*>(quota + e);
+  __shared__ uint32_t s_epoch;
+  __shared__ int s_ok;
+
+  if (threadIdx.x == 0) s_epoch = ld_acquire_gpu(&ws->epoch) + 1;
+  for (int i = threadIdx.x; i < e; i += kBlock) hist[i] = 0;
+  __syncthreads();
+  const uint32_t epoch = s_epoch;
+  const int parity = epoch & 1;
+  int* total_g = ws_total(ws, parity, e);
+
+  const long long begin = slice_begin(n, p, n_cta, kBlock), end = slice_begin(n, p + 1, n_cta, kBlock);
+  histogram_slice(idx, begin, end, e, hist, status);
+  __syncthreads();
+  for (int i = threadIdx.x; i < e; i += kBlock) {
+    const int c = hist[i];
+    cur[i] = c ? atomicAdd(&total_g[i], c) : 0;
+  }
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) atomicAdd(&ws->arrive, 1u);
+
+  if (p == 0) {
+    if (threadIdx.x == 0) {
+      s_ok = bounded_wait_ge<false>(&ws->arrive, (uint32_t)n_cta, grid_timeout_ns);
+      if (!s_ok) {
+        atomicAdd(&status[kStTimeouts], 1);
+        raise_status(status, kErrGridTimeout, kPhCount, (int)ld_acquire_gpu(&ws->arrive));
+      }
+      status[kStLpIters] = 0;
+    }
+    __syncthreads();
+    int* mine = quota;                           // reuse: local totals
+    int* summed = reinterpret_cast<int*>(phys);  // reuse: group-wide totals (needs E ints of the 2E)
+    int* other = ws_total(ws, parity ^ 1, e);
+    for (int i = threadIdx.x; i < e; i += kBlock) {
+      mine[i] = __ldcg(&total_g[i]);
+      other[i] = 0;  // ready for the next launch
+    }
+    __syncthreads();
+    if (ex.n_ranks > 1) {
+      const unsigned miss = exchange_counts(ex, epoch, e, mine, summed);
+      if (miss && threadIdx.x == 0) {
+        atomicAdd(&status[kStTimeouts], 1);
+        raise_status(status, kErrPeerTimeout, kPhExchange, (int)miss);
+      }
+    } else {
+      for (int i = threadIdx.x; i < e; i += kBlock) summed[i] = mine[i];
+      __syncthreads();
+    }
+    int* glob = ws_global(ws, e);
+    for (int i = threadIdx.x; i < e; i += kBlock) glob[i] = summed[i];
+    solve_groups<GP, D>(summed, tp, 0, kWarps * (32 / GP), prm, probs, avail, status);
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) st_release_gpu(&ws->lp_done, epoch);
+  }
+
+  if (threadIdx.x == 0) {
+    s_ok = bounded_wait_ge<false>(&ws->lp_done, epoch, grid_timeout_ns);
+    if (!s_ok) {
+      atomicAdd(&status[kStTimeouts], 1);
+      raise_status(status, kErrLpTimeout, kPhRedirect, p);
+    }
+  }
+  __syncthreads();
+  const bool have_probs = s_ok;
+  for (int i = threadIdx.x; i < e; i += kBlock) {
+    const int tot = __ldcg(&total_g[i]);
+    hist[i] = tot;
+    const int edge = tp.log2edge[i];
+    quota[i] = have_probs ? quota_of(tot, edge, probs) : (edge < 0 ? tot : tot / 2);
+    phys[i] = reinterpret_cast<const int2*>(tp.log2phy)[i];
+  }
+  __syncthreads();
+  redirect_slice(idx, begin, end, e, cur, hist, quota, phys, out);
+
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    if (atomicAdd(&ws->exit_cnt, 1u) == (unsigned)n_cta - 1) {
+      ws->arrive = 0;
+      ws->exit_cnt = 0;
+      atomicAdd(&status[kStCalls], 1);
+      st_release_gpu(&ws->epoch, epoch);
+    }
+  }
+}
+
+}  // namespace lplb

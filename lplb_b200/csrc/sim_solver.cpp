@@ -1,0 +1,56 @@
+// CPU build of the warp-level LP solver (see host_sim.h): a C entry point for ctypes.
+// Compiled with -DLPLB_HOST_SIM by the CPU tests; not part of the GPU extension.
+#define LPLB_HOST_SIM 1
+#include "lp_solver.cuh"
+
+namespace {
+
+template <int GP, int D>
+void solve_batch(int g, const int* r2o, const int* o2r, int nb, const double* w, const double* fixed, int max_iters,
+                 double tol, double* f_out, int* iters, int* converged) {
+  constexpr int kSeg = 32 / GP;
+  for (int b0 = 0; b0 < nb; b0 += kSeg) {
+    lplb_sim::run_warp([&](int lane) {
+      const int seg = lane / GP, li = lane % GP, b = b0 + seg;
+      const bool live = b < nb && li < g;
+      double wl[D], f[D], fx = 0.0;
+      int src[D], dst[D];
+      for (int d = 0; d < D; ++d) {
+        wl[d] = 0.0;
+        src[d] = dst[d] = li;
+      }
+      if (live) {
+        fx = fixed[(size_t)b * g + li];
+        for (int d = 0; d < D; ++d) {
+          wl[d] = w[((size_t)b * g + li) * D + d];
+          src[d] = r2o[li * D + d];
+          dst[d] = o2r[li * D + d];
+        }
+      }
+      const lplb::IpmOutcome res = lplb::ipm_solve_segment<GP, D>(li, wl, fx, src, dst, lplb::IpmParams{max_iters, tol}, f);
+      if (live) {
+        for (int d = 0; d < D; ++d) f_out[((size_t)b * g + li) * D + d] = f[d];
+        if (li == 0) {
+          iters[b] = res.iters;
+          converged[b] = res.converged ? 1 : 0;
+        }
+      }
+    });
+  }
+}
+
+}  // namespace
+
+extern "C" int lplb_sim_solve(int g, int d, const int* r2o, const int* o2r, int nb, const double* w,
+                              const double* fixed, int max_iters, double tol, double* f_out, int* iters,
+                              int* converged) {
+  const int gp = g <= 8 ? 8 : (g <= 16 ? 16 : 32);
+#define LPLB_CASE(GP_, D_)                                                                             \
+  if (gp == GP_ && d == D_) {                                                                          \
+    solve_batch<GP_, D_>(g, r2o, o2r, nb, w, fixed, max_iters, tol, f_out, iters, converged);          \
+    return 0;                                                                                          \
+  }
+  LPLB_CASE(8, 1) LPLB_CASE(8, 2) LPLB_CASE(8, 4) LPLB_CASE(16, 2) LPLB_CASE(32, 2) LPLB_CASE(32, 1)
+#undef LPLB_CASE
+  return 1;
+}

@@ -1,0 +1,382 @@
+"""Public API: the per-batch token re-router for expert-parallel MoE.
+
+``Planner`` keeps the constructor arguments, method names and tensor shapes of the
+reference's ``lplb.Planner`` (reference ``lplb/planner.py:38-266``) so that a training
+loop written against it runs unchanged:
+
+.. code-block:: python
+
+    planner = Planner(r2o, n_physical, n_logical, group=ep_group)
+    planner.update_redundancy_mapping(history)         # every N steps
+    phys = planner.run(indices, avail_counter, n_sms)  # every batch
+
+Differences that a user can observe, all deliberate:
+
+* ``run`` is one kernel launch (histogram, NVLink statistics exchange, LP, redirect) when
+  the statistics travel over peer memory or not at all; the three-stage pipeline with
+  ``torch.distributed.all_reduce`` remains as ``comm="nccl"``.
+* The shares come from a primal-dual interior-point method that stops on a duality-gap
+  test (``tol``), not from five affine-scaling steps; they are always inside ``[0, 1]``.
+* ``avail_counter`` may be int32 or int64 and counts converged groups per call.
+* ``device``/``n_nodes`` are explicit, so everything up to and including the LP runs on
+  a CPU device too (used by the CPU test-suite).
+* Waits on other GPUs are bounded; their outcome is visible through ``check_status``.
+"""
+
+from __future__ import annotations
+
+import logging
+from typing import Any
+
+import torch
+
+from . import lp as _lp
+from .mapping import ExpertMapping, build_mapping
+from .ops import reference as _ref
+from .topology import invert_r2o, validate_r2o
+
+log = logging.getLogger("lplb_b200")
+
+__all__ = ["Planner", "PlannerStatus"]
+
+_ERR_NAMES = {
+    0: "ok",
+    1: "grid_timeout",
+    2: "peer_timeout",
+    3: "lp_timeout",
+    4: "bad_index",
+    5: "lp_not_converged",
+}
+_PHASE_NAMES = {0: "-", 1: "count", 2: "exchange", 3: "solve", 4: "redirect"}
+
+
+class PlannerStatus(dict):
+    """Decoded status block of the native engine (see ``csrc/common.cuh``)."""
+
+    @property
+    def ok(self) -> bool:
+        return self["error"] == "ok"
+
+
+class Planner:
+    def __init__(
+        self,
+        redundant_to_original: torch.Tensor,
+        n_routed_experts: int,
+        n_logical_routed_experts: int,
+        ep_size: int | None = None,
+        group: "torch.distributed.ProcessGroup | None" = None,
+        *,
+        device: torch.device | str | None = None,
+        n_nodes: int | None = None,
+        comm: str = "auto",
+        max_iters: int = 24,
+        tol: float = 1e-4,
+        peer_timeout_us: float = 1e6,
+        grid_timeout_us: float = 1e6,
+        allow_self_edges: bool = False,
+    ) -> None:
+        """
+        :param redundant_to_original: ``[group_size, num_redundants]``; rank ``i``'s
+            ``d``-th redundant slot is a copy of rank ``r2o[i, d]``'s ``d``-th
+            replicated expert.  Every column must be a permutation of the ranks.  The
+            real number of redundant experts per rank may be a multiple ``C`` of
+            ``num_redundants``; ``C`` experts then share one LP variable.
+        :param n_routed_experts: physical experts in total (logical + redundant).
+        :param n_logical_routed_experts: logical experts in total.
+        :param ep_size: EP ranks; defaults to ``group.size()``.
+        :param group: EP process group.  ``None`` means statistics are not exchanged.
+        :param device: where the planner's tensors live; default ``cuda`` if available.
+        :param n_nodes: nodes seen by the placement balancer; default
+            ``max(1, ep_size // gpus_per_host)``.
+        :param comm: ``"p2p"`` exchanges statistics inside the kernel over NVLink peer
+            memory, ``"nccl"`` uses ``torch.distributed.all_reduce`` between kernels,
+            ``"none"`` never exchanges, ``"auto"`` picks ``p2p`` when every rank of the
+            group is on this host and falls back to ``nccl``.
+        :param max_iters, tol: interior-point iteration cap and relative duality gap.
+        :param peer_timeout_us, grid_timeout_us: budgets of the in-kernel waits.
+        """
+        if device is None:
+            device = "cuda" if torch.cuda.is_available() else "cpu"
+        self.device = torch.device(device)
+        if self.device.type == "cuda" and self.device.index is None:
+            self.device = torch.device("cuda", torch.cuda.current_device())
+
+        validate_r2o(redundant_to_original, allow_self_edges=allow_self_edges)
+        self.r2o = redundant_to_original.to(self.device, torch.int32).contiguous()
+        self.o2r = invert_r2o(redundant_to_original.cpu()).to(self.device)
+        self.group_size, self.num_redundants = int(self.r2o.shape[0]), int(self.r2o.shape[1])
+
+        self.n_routed_experts = int(n_routed_experts)
+        self.n_logical_routed_experts = int(n_logical_routed_experts)
+        if ep_size is None:
+            if group is None:
+                raise ValueError("ep_size must be provided when group is None")
+            ep_size = group.size()
+        self.ep_size = int(ep_size)
+        if self.ep_size % self.group_size:
+            raise ValueError(f"ep_size {self.ep_size} is not a multiple of the topology's {self.group_size} ranks")
+        self.n_group = self.ep_size // self.group_size
+        if self.n_routed_experts % self.ep_size or self.n_logical_routed_experts % self.ep_size:
+            raise ValueError("expert counts must be multiples of ep_size")
+        self.n_local_routed_experts = self.n_routed_experts // self.ep_size
+        self.n_local_logical_routed_experts = self.n_logical_routed_experts // self.ep_size
+        extra = self.n_local_routed_experts - self.n_local_logical_routed_experts
+        if extra <= 0 or extra % self.num_redundants:
+            raise ValueError(
+                f"{extra} redundant experts per rank cannot be split over {self.num_redundants} topology slots"
+            )
+        self.combined_redundant_experts = extra // self.num_redundants
+
+        if n_nodes is None:
+            per_host = torch.cuda.device_count() if torch.cuda.is_available() else 0
+            n_nodes = max(1, self.ep_size // per_host) if per_host else 1
+        self.n_nodes = int(n_nodes)
+        self.max_iters, self.tol = int(max_iters), float(tol)
+        self.ep_group = group
+        self.deep_ep_initialized = False  # name kept from the reference: "in-kernel exchange is live"
+        self._n_sms_default: int | None = None
+
+        self._engine = None
+        if self.device.type == "cuda":
+            from . import _native
+
+            native = _native.load()  # raises if the extension is missing: no silent fallback on a GPU
+            self._engine = native.PlannerEngine(
+                self.n_group,
+                self.group_size,
+                self.num_redundants,
+                self.n_local_logical_routed_experts,
+                self.combined_redundant_experts,
+                self.device.index,
+            )
+            self._engine.set_topology(self.r2o, self.o2r)
+            self._engine.set_params(self.max_iters, self.tol, float(peer_timeout_us), float(grid_timeout_us))
+
+        self.mapping: ExpertMapping
+        self.phy2log: torch.Tensor
+        self.update_redundancy_mapping()
+
+        if comm not in ("auto", "p2p", "nccl", "none"):
+            raise ValueError(f"unknown comm mode {comm!r}")
+        self.comm = "none"
+        if group is not None and comm != "none" and group.size() > 1:
+            self.comm = "nccl"
+            if comm in ("auto", "p2p") and self._engine is not None:
+                try:
+                    self.init_peer_exchange()
+                except Exception as exc:
+                    if comm == "p2p":
+                        raise
+                    log.warning("peer-memory exchange unavailable (%s); using torch.distributed.all_reduce", exc)
+
+    # ------------------------------------------------------------------ communicator
+    def init_peer_exchange(self) -> None:
+        """Bring up the in-kernel NVLink statistics exchange (collective over the group).
+
+        Allocates this rank's receive buffers, all-gathers CUDA-IPC handles through
+        ``torch.distributed`` and maps every peer.  Fails if a rank of the group lives
+        on another host.  Counterpart of the reference's ``init_comm``
+        (reference ``csrc/plugin.cpp:357-456``), minus NVSHMEM.
+        """
+        from .parallel.exchange import open_peer_exchange
+
+        if self.deep_ep_initialized:
+            return
+        if self._engine is None or self.ep_group is None:
+            raise RuntimeError("peer exchange needs a CUDA device and a process group")
+        open_peer_exchange(self._engine, self.ep_group, self.device)
+        self.deep_ep_initialized = True
+        self.comm = "p2p"
+
+    def init_from_deep_ep(self, buffer: Any = None) -> None:
+        """Switch to the in-kernel exchange (API of reference ``lplb/planner.py:104-113``).
+
+        The reference borrows DeepEP's NVSHMEM state here.  This build needs nothing from
+        the buffer: all ranks of one NVLink domain are reached through peer memory that
+        the planner maps itself, so the argument is accepted and ignored.
+        """
+        self.init_peer_exchange()
+
+    def reset_exchange(self) -> None:
+        """Collective: re-zero epochs, flags and buffers on every rank (e.g. after a timeout)."""
+        if self._engine is None:
+            return
+        if self.ep_group is not None:
+            torch.distributed.barrier(group=self.ep_group)
+        self._engine.reset_exchange()
+        if self.ep_group is not None:
+            torch.distributed.barrier(group=self.ep_group)
+
+    # ------------------------------------------------------------------ slow path
+    def update_redundancy_mapping(
+        self, workload: torch.Tensor | None = None
+    ) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+        """Re-place experts from load history and rebuild every lookup table.
+
+        Returns ``(phy2log [P], log2phy [E, 2], logcnt [E])`` int32 on the planner's
+        device (reference ``lplb/planner.py:115-182``).  Moving the expert *weights* to
+        match ``phy2log`` is the caller's job, as in the reference.
+        """
+        mapping = build_mapping(
+            self.r2o,
+            self.n_group,
+            self.n_local_logical_routed_experts,
+            self.combined_redundant_experts,
+            workload,
+            n_nodes=self.n_nodes,
+        )
+        assert mapping.phy2log.numel() == self.n_routed_experts
+        self.mapping = mapping.to(self.device)
+        self.phy2log = self.mapping.phy2log
+        if self._engine is not None:
+            self._engine.set_mapping(self.mapping.phy2log, self.mapping.log2phy, self.mapping.log2edge)
+        return self.mapping.phy2log, self.mapping.log2phy, self.mapping.logcnt
+
+    # ------------------------------------------------------------------ stages
+    def _default_sms(self) -> int:
+        if self._n_sms_default is None:
+            if self.device.type == "cuda":
+                self._n_sms_default = torch.cuda.get_device_properties(self.device).multi_processor_count
+            else:
+                self._n_sms_default = 8
+        return self._n_sms_default
+
+    def count_workload(self, idx: torch.Tensor, n_sms: int) -> tuple[torch.Tensor, torch.Tensor]:
+        """Count logical expert ids in ``idx`` (``-1`` is skipped).
+
+        :return: ``(counts [E] int32, inclusive prefix over the n_sms token slices [n_sms, E])``
+            (reference ``lplb/planner.py:184-194``).
+        """
+        if self._engine is not None:
+            return self._engine.count_idx(idx.contiguous(), int(n_sms))
+        return _ref.count_reference(idx, self.n_logical_routed_experts, int(n_sms))
+
+    def solve_probs(self, workload: torch.Tensor, avail_counter: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+        """Solve every group's LP for the given per-expert statistics.
+
+        :param workload: ``numel == n_logical`` counts of this rank (summed over the
+            group first when a communicator is set).
+        :param avail_counter: one-element integer tensor, incremented once per group
+            whose LP converged.
+        :return: ``(probs [NG, G, D] float32, workload / max(workload) [NG, G, Ll] float32)``
+            (reference ``lplb/planner.py:196-217`` returns the same pair).
+        """
+        shape = (self.n_group, self.group_size, self.n_local_logical_routed_experts)
+        if self._engine is not None:
+            wl = workload.reshape(-1).to(torch.int32).contiguous()
+            if self.comm == "p2p":
+                wl = self._engine.all_reduce_counts(wl)
+            elif self.comm == "nccl":
+                wl = wl.clone()
+                torch.distributed.all_reduce(wl, group=self.ep_group)
+            probs, normalised = self._engine.solve(wl, avail_counter)
+            return probs, normalised.view(shape)
+
+        wl = workload.reshape(-1).to(torch.int64)
+        if self.comm == "nccl":
+            wl = wl.clone()
+            torch.distributed.all_reduce(wl, group=self.ep_group)
+        w, fixed = _lp.bundle_loads(
+            wl.double(),
+            self.phy2log,
+            self.n_group,
+            self.group_size,
+            self.num_redundants,
+            self.n_local_logical_routed_experts,
+            self.combined_redundant_experts,
+        )
+        res = _lp.solve_ipm(w, fixed, self.r2o.cpu(), max_iters=self.max_iters, tol=self.tol)
+        avail_counter += int(res.converged.sum())
+        peak = wl.max().clamp_min(1).float()
+        return res.f.float().to(self.device), (wl.float() / peak).view(shape)
+
+    def weighted_select_target(
+        self,
+        idx: torch.Tensor,
+        o_weight: torch.Tensor,
+        local_workload_by_sm: torch.Tensor,
+        n_sms: int,
+    ) -> torch.Tensor:
+        """Rewrite logical ids to physical ids so that a share ``o_weight`` of every
+        replicated expert's local tokens stays on the original
+        (reference ``lplb/planner.py:219-243``).  ``n_sms`` must equal the value given to
+        ``count_workload``."""
+        if self._engine is not None:
+            return self._engine.map_idx(
+                idx.contiguous(), o_weight.float().contiguous(), local_workload_by_sm, int(n_sms)
+            )
+        return _ref.redirect_reference(idx, o_weight, self.mapping.log2phy, self.mapping.log2edge)
+
+    # ------------------------------------------------------------------ hot path
+    def run(self, idx: torch.Tensor, avail_counter: torch.Tensor, n_sms: int | None = None) -> torch.Tensor:
+        """Logical expert ids ``[-1, E)`` in, physical expert ids ``[-1, P)`` out, same shape
+        (reference ``lplb/planner.py:245-266``)."""
+        if n_sms is None:
+            n_sms = self._default_sms()
+        if self._engine is not None and self.comm in ("p2p", "none"):
+            return self._engine.run_fused(idx.contiguous(), avail_counter, int(n_sms), self.comm == "p2p")
+        local, by_sm = self.count_workload(idx, n_sms)
+        probs, _ = self.solve_probs(local, avail_counter)
+        return self.weighted_select_target(idx, probs, by_sm, n_sms)
+
+    def run_staged(self, idx: torch.Tensor, avail_counter: torch.Tensor, n_sms: int | None = None) -> torch.Tensor:
+        """The three-launch pipeline regardless of ``comm`` (baseline for measurements)."""
+        if n_sms is None:
+            n_sms = self._default_sms()
+        local, by_sm = self.count_workload(idx, n_sms)
+        probs, _ = self.solve_probs(local, avail_counter)
+        return self.weighted_select_target(idx, probs, by_sm, n_sms)
+
+    @property
+    def last_probs(self) -> torch.Tensor | None:
+        """Shares ``[NG, G, D]`` computed by the most recent fused ``run``."""
+        return None if self._engine is None else self._engine.last_probs()
+
+    # ------------------------------------------------------------------ observability
+    def check_status(self, clear: bool = False) -> PlannerStatus:
+        """Read the engine's status block (one small device-to-host copy)."""
+        if self._engine is None:
+            return PlannerStatus(error="ok", phase="-", detail=0, calls=0, lp_iters=0, lp_failures=0, timeouts=0, bad_indices=0)
+        raw = self._engine.status().cpu().tolist()
+        out = PlannerStatus(
+            error=_ERR_NAMES.get(raw[0], str(raw[0])),
+            phase=_PHASE_NAMES.get(raw[1], str(raw[1])),
+            detail=raw[2],
+            calls=raw[3],
+            lp_iters=raw[4],
+            lp_failures=raw[5],
+            timeouts=raw[6],
+            bad_indices=raw[7],
+        )
+        if clear:
+            self._engine.status().zero_()
+        return out
+
+    # ------------------------------------------------------------------ checkpointing
+    def state_dict(self) -> dict[str, Any]:
+        """Everything needed to resume with the same placement (the reference keeps no
+        such state: its ``phy2log`` lives only on the object, ``lplb/planner.py:180``)."""
+        return {
+            "r2o": self.r2o.cpu(),
+            "phy2log": self.mapping.phy2log.cpu(),
+            "log2phy": self.mapping.log2phy.cpu(),
+            "logcnt": self.mapping.logcnt.cpu(),
+            "log2edge": self.mapping.log2edge.cpu(),
+            "n_routed_experts": self.n_routed_experts,
+            "n_logical_routed_experts": self.n_logical_routed_experts,
+            "ep_size": self.ep_size,
+        }
+
+    def load_state_dict(self, state: dict[str, Any]) -> None:
+        if not torch.equal(state["r2o"].int(), self.r2o.cpu()):
+            raise ValueError("checkpoint was written for a different topology")
+        for key in ("n_routed_experts", "n_logical_routed_experts", "ep_size"):
+            if int(state[key]) != getattr(self, key):
+                raise ValueError(f"checkpoint {key}={state[key]} does not match this planner")
+        self.mapping = ExpertMapping(
+            state["phy2log"].int(), state["log2phy"].int(), state["logcnt"].int(), state["log2edge"].int()
+        ).to(self.device)
+        self.phy2log = self.mapping.phy2log
+        if self._engine is not None:
+            self._engine.set_mapping(self.mapping.phy2log, self.mapping.log2phy, self.mapping.log2edge)

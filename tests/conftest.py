@@ -1,0 +1,31 @@
+import os
+import sys
+
+import pytest
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a CUDA device (B200); deselected on CPU hosts")
+    config.addinivalue_line("markers", "multigpu: needs at least two CUDA devices")
+
+
+def pytest_collection_modifyitems(config, items):
+    if torch.cuda.is_available():
+        n = torch.cuda.device_count()
+        skip_multi = pytest.mark.skip(reason="needs >= 2 GPUs")
+        for item in items:
+            if "multigpu" in item.keywords and n < 2:
+                item.add_marker(skip_multi)
+        return
+    skip = pytest.mark.skip(reason="no CUDA device")
+    for item in items:
+        if "gpu" in item.keywords:
+            item.add_marker(skip)
+
+
+@pytest.fixture
+def cuda_device():
+    return torch.device("cuda", 0)

@@ -1,0 +1,119 @@
+import numpy as np
+import pytest
+import torch
+
+from lplb_b200 import Planner, lp, topology
+from tests.helpers import SOLVE_CONFIGS, balance_after, synthetic_loads
+
+
+def _random_instance(r2o, ll, seed, n=8):
+    g, d = r2o.shape
+    cnt = ((torch.randn(n, g, ll, generator=torch.Generator().manual_seed(seed), dtype=torch.float64) * 0.3 + 1).clamp_min(0) * 4096).floor()
+    return cnt[:, :, :d].contiguous(), cnt[:, :, d:].sum(-1)
+
+
+@pytest.mark.parametrize("name", ["cube", "ring8", "hypercube", "torus8x4", "torus2x4"])
+def test_ipm_matches_highs(name):
+    r2o = topology.by_name(name)
+    w, fixed = _random_instance(r2o, 8, seed=11)
+    res = lp.solve_ipm(w, fixed, r2o, tol=1e-6)
+    assert bool(res.converged.all())
+    assert bool(((res.f >= 0) & (res.f <= 1)).all())
+    for i in range(w.shape[0]):
+        _, t_opt = lp.solve_highs(w[i], fixed[i], r2o)
+        assert float(res.t[i]) >= t_opt * (1 - 1e-9)
+        assert (float(res.t[i]) - t_opt) / t_opt < 1e-5
+        assert int(res.iters[i]) <= 12
+
+
+def test_standard_form_agrees_with_compact_form():
+    from scipy.optimize import linprog
+
+    r2o = topology.cube()
+    w, fixed = _random_instance(r2o, 8, seed=3, n=2)
+    for i in range(2):
+        a, b, c = lp.standard_form(w[i], fixed[i], r2o, big_m=1e6)
+        res = linprog(c.numpy(), A_eq=a.numpy(), b_eq=b.numpy(), bounds=[(0, None)] * a.shape[1], method="highs")
+        assert res.status == 0
+        _, t_opt = lp.solve_highs(w[i], fixed[i], r2o)
+        assert abs(res.fun - t_opt) / t_opt < 1e-7
+        # x = 1 is feasible by construction of the artificial column
+        assert torch.allclose(a @ torch.ones(a.shape[1], dtype=torch.float64), b)
+
+
+def test_degenerate_loads():
+    r2o = topology.cube()
+    g, d = r2o.shape
+    w = torch.zeros(5, g, d, dtype=torch.float64)
+    fixed = torch.zeros(5, g, dtype=torch.float64)
+    w[1, 0, 0] = 1000  # one hot bundle
+    fixed[2, 3] = 500  # one hot fixed expert: nothing can move
+    w[3] = 7
+    fixed[3] = 3  # all equal
+    w[4, 2, 0], w[4, 5, 1], fixed[4] = 1, 2**30, 1  # huge dynamic range
+    res = lp.solve_ipm(w, fixed, r2o)
+    assert bool(res.converged.all()) and not bool(torch.isnan(res.f).any())
+    assert torch.equal(res.f[0], torch.ones(g, d, dtype=torch.float64))  # empty group keeps everything
+    assert abs(float(res.t[1]) - 500) / 500 < 1e-3  # split the hot bundle in half
+    assert abs(float(res.t[2]) - 500) < 1e-6
+    assert abs(float(res.t[3]) - 17) / 17 < 1e-3
+    for i in (1, 3, 4):
+        _, t_opt = lp.solve_highs(w[i], fixed[i], r2o)
+        assert (float(res.t[i]) - t_opt) / t_opt < 1e-3
+
+
+def test_config2_shape_gap_is_below_target():
+    # Dirichlet(0.3) multinomial over 128 experts, 16 per rank, heaviest two replicated
+    rng = np.random.default_rng(0)
+    r2o = topology.cube()
+    ws, fs = [], []
+    for _ in range(40):
+        p = rng.dirichlet(np.full(128, 0.3))
+        cnt = -np.sort(-rng.multinomial(32768 * 8, p).reshape(8, 16).astype(np.float64), axis=1)
+        ws.append(cnt[:, :2])
+        fs.append(cnt[:, 2:].sum(1))
+    w, fixed = torch.tensor(np.array(ws)), torch.tensor(np.array(fs))
+    res = lp.solve_ipm(w, fixed, r2o, tol=1e-4)
+    assert bool(res.converged.all())
+    gaps = []
+    for i in range(len(w)):
+        _, t_opt = lp.solve_highs(w[i], fixed[i], r2o)
+        gaps.append((float(res.t[i]) - t_opt) / t_opt)
+    assert max(gaps) < 1e-3 and min(gaps) > -1e-9
+
+
+def test_affine_scaling_restatement_runs_and_is_worse_than_ipm():
+    r2o = topology.cube()
+    w, fixed = _random_instance(r2o, 8, seed=21, n=6)
+    worse = 0
+    for i in range(6):
+        _, t_opt = lp.solve_highs(w[i], fixed[i], r2o)
+        _, t_ref, ok = lp.affine_scaling_reference(w[i], fixed[i], r2o)
+        t_ipm = float(lp.solve_ipm(w[i], fixed[i], r2o).t[0])
+        assert t_ref >= t_opt * (1 - 1e-6)
+        worse += t_ref >= t_ipm - 1e-9
+    assert worse >= 4
+
+
+@pytest.mark.parametrize("name,r2o,n_logical,ep_size,n_red,reorder,bound", SOLVE_CONFIGS)
+def test_planner_solve_quality_cpu(name, r2o, n_logical, ep_size, n_red, reorder, bound):
+    # CPU restatement of reference tests/test_solve.py:24-89
+    planner = Planner(r2o, n_logical + n_red * ep_size, n_logical, ep_size, device="cpu")
+    history, current = synthetic_loads(n_logical, seed=41)
+    phy2log, _, _ = planner.update_redundancy_mapping(history if reorder else None)
+    avail = torch.zeros((), dtype=torch.int32)
+    probs, normalised = planner.solve_probs(current, avail)
+    assert int(avail) == planner.n_group
+    assert probs.shape == (planner.n_group, planner.group_size, planner.num_redundants)
+    assert float(normalised.max()) == 1.0
+    # the reference's bound for this configuration (the draw differs: its RNG is CUDA's) ...
+    assert balance_after(planner, phy2log, current, probs) < bound
+    # ... and, stronger, every group sits within 1e-3 of its true LP optimum
+    w, fixed = lp.bundle_loads(
+        current.double(), phy2log, planner.n_group, planner.group_size, planner.num_redundants,
+        planner.n_local_logical_routed_experts, planner.combined_redundant_experts,
+    )
+    realised = lp.rank_loads(probs.double(), w, fixed, r2o).max(-1).values
+    for grp in range(planner.n_group):
+        _, t_opt = lp.solve_highs(w[grp], fixed[grp], r2o)
+        assert (float(realised[grp]) - t_opt) / t_opt < 1e-3
