@@ -1,0 +1,396 @@
+#!/usr/bin/env python
+"""Headline benchmark: ``planner.run`` latency on DeepSeek-V3-shaped gating, EP8 Cube.
+
+256 logical + 16 redundant experts (2 per rank of the 8-rank Cube), top-8, 4096 tokens
+per rank.  Indices are the top-k of bf16 logits ~ N(0,1) plus a per-expert bias ~ N(0,1)
+that is redrawn every 50 steps; everything is seeded per step.  With N < 8 GPUs the LP
+still covers the 8-rank Cube (``ep_size=8``); the N real ranks each contribute 4096
+tokens and exchange their statistics, so per-GPU work is fixed ("weak" scaling).
+
+``python bench.py --gpus N --steps K --warmup W`` prints one JSON line on rank 0.
+For N > 1 launch through ``python -m torch.distributed.run --nproc-per-node N``.
+``--impl reference`` runs the unmodified reference from ``baseline/_ref`` instead.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+N_LOGICAL = 256
+EP_SIZE = 8
+RED_PER_RANK = 2
+TOKENS_PER_RANK = 4096
+TOP_K = 8
+BIAS_PERIOD = 50
+PUBLISHED_SOLVER_US = 100.0  # reference README.md:70, solver only, unstated hardware
+METRIC = "planner.run us (device, max over ranks), EP8 Cube, 4096 tokens/rank x top-8"
+
+
+def make_indices(step: int, rank: int, device: torch.device) -> torch.Tensor:
+    """Logical expert ids ``[4096, 8]`` int64 for one step of one rank."""
+    gb = torch.Generator(device=device).manual_seed(1_000_003 * (step // BIAS_PERIOD) + 17)
+    bias = torch.randn(N_LOGICAL, device=device, generator=gb)
+    gl = torch.Generator(device=device).manual_seed(7919 * step + 104_729 * rank + 1)
+    logits = torch.randn(TOKENS_PER_RANK, N_LOGICAL, device=device, generator=gl) + bias
+    return logits.bfloat16().topk(TOP_K, dim=-1).indices
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons through NVML while the timed region runs."""
+
+    def __init__(self, index: int, period_s: float = 0.004):
+        self.index, self.period = index, period_s
+        self.samples: list[int] = []
+        self.reasons: set[str] = set()
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            self._nvml = pynvml
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self._nvml = None
+
+    def _loop(self):
+        nv = self._nvml
+        names = {
+            0x8: "hw_slowdown",
+            0x40: "hw_thermal_slowdown",
+            0x20: "sw_thermal_slowdown",
+            0x4: "sw_power_cap",
+            0x80: "hw_power_brake_slowdown",
+        }
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM))
+                mask = nv.nvmlDeviceGetCurrentClocksEventReasons(self._h)
+                for bit, name in names.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(self.period)
+
+    def __enter__(self):
+        if self._nvml is not None:
+            self._thread = threading.Thread(target=self._loop, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+
+    def summary(self) -> dict:
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": ["unsampled"]}
+        return {
+            "sm_mhz": int(statistics.median(self.samples)),
+            "sm_max_mhz": self.max_mhz,
+            "reasons": sorted(self.reasons),
+            "samples": len(self.samples),
+        }
+
+
+def physical_gpu_index(local: int) -> int:
+    vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+    if vis:
+        try:
+            return int(vis.split(",")[local])
+        except (ValueError, IndexError):
+            pass
+    return local
+
+
+def dist_setup(n_gpus: int):
+    import torch.distributed as dist
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if n_gpus > 1 and world != n_gpus:
+        raise SystemExit(
+            f"--gpus {n_gpus} needs {n_gpus} ranks: launch with python -m torch.distributed.run "
+            f"--nnodes=1 --nproc-per-node {n_gpus} --master-addr 127.0.0.1 bench.py --gpus {n_gpus}"
+        )
+    torch.cuda.set_device(local)
+    group = None
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        group = dist.group.WORLD
+    return rank, world, local, group
+
+
+def rank_max(values: torch.Tensor, group) -> torch.Tensor:
+    if group is not None:
+        import torch.distributed as dist
+
+        dist.all_reduce(values, op=dist.ReduceOp.MAX, group=group)
+    return values
+
+
+def post_balance(planner_like, out: torch.Tensor, group, pl: int) -> float:
+    """max/mean physical-rank load over the whole job after redirect."""
+    load = torch.bincount(out.reshape(-1).clamp_min(0) // pl, weights=(out.reshape(-1) >= 0).double(), minlength=EP_SIZE)
+    if group is not None:
+        import torch.distributed as dist
+
+        dist.all_reduce(load, group=group)
+    return float(load.max() / load.mean())
+
+
+def run_ours(args) -> dict:
+    from lplb_b200 import Planner, cube
+
+    rank, world, local, group = dist_setup(args.gpus)
+    dev = torch.device("cuda", local)
+    planner = Planner(
+        cube(), N_LOGICAL + RED_PER_RANK * EP_SIZE, N_LOGICAL, EP_SIZE, group, device=dev, comm=args.comm
+    )
+    n_sms = args.n_sms or torch.cuda.get_device_properties(dev).multi_processor_count
+    pl = planner.n_local_routed_experts
+
+    total_steps = args.warmup + args.steps
+    idx_dev = [make_indices(s, rank, dev) for s in range(total_steps)]
+    idx_pinned = [t.cpu().pin_memory() for t in idx_dev]
+    out_pinned = torch.empty_like(idx_pinned[0]).pin_memory()
+    avail = torch.zeros(1, dtype=torch.int32, device=dev)
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)  # 2x the 126 MB L2
+
+    # placement from the statistics of the first bias period, as a training loop would
+    hist = torch.zeros(N_LOGICAL, dtype=torch.int64, device=dev)
+    for s in range(min(8, total_steps)):
+        hist += torch.bincount(idx_dev[s].reshape(-1), minlength=N_LOGICAL)
+    if group is not None:
+        import torch.distributed as dist
+
+        dist.all_reduce(hist, group=group)
+    planner.update_redundancy_mapping(hist)
+
+    def barrier():
+        if group is not None:
+            import torch.distributed as dist
+
+            dist.barrier(group=group)
+        torch.cuda.synchronize(dev)
+
+    # ---- device-timed kernel path -------------------------------------------------------
+    for s in range(args.warmup):
+        flush.fill_(s & 0xFF)
+        planner.run(idx_dev[s], avail, n_sms)
+    starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    ends = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    barrier()
+    with ClockSampler(physical_gpu_index(local)) as clocks:
+        for k in range(args.steps):
+            flush.fill_(k & 0xFF)  # evict L2 between timed iterations
+            starts[k].record()
+            out = planner.run(idx_dev[args.warmup + k], avail, n_sms)
+            ends[k].record()
+        barrier()
+    per_step_ms = torch.tensor([a.elapsed_time(b) for a, b in zip(starts, ends)], dtype=torch.float64, device=dev)
+    per_step_ms = rank_max(per_step_ms, group)
+    ms_per_step = float(per_step_ms.mean())
+    status = planner.check_status()
+    balance_after = post_balance(planner, out, group, pl)
+    naive = planner.mapping.log2phy[idx_dev[-1].reshape(-1), 0].long()
+    balance_before = post_balance(planner, naive, group, pl)
+
+    # ---- three-launch pipeline with torch.distributed.all_reduce, same inputs ----------------
+    staged = Planner(
+        cube(), N_LOGICAL + RED_PER_RANK * EP_SIZE, N_LOGICAL, EP_SIZE, group, device=dev,
+        comm="nccl" if group is not None else "none",
+    )
+    staged.load_state_dict(planner.state_dict())
+    for s in range(args.warmup):
+        staged.run_staged(idx_dev[s], avail, n_sms)
+    barrier()
+    for k in range(args.steps):
+        flush.fill_(k & 0xFF)
+        starts[k].record()
+        staged.run_staged(idx_dev[args.warmup + k], avail, n_sms)
+        ends[k].record()
+    barrier()
+    staged_ms = torch.tensor([a.elapsed_time(b) for a, b in zip(starts, ends)], dtype=torch.float64, device=dev)
+    staged_ms = float(rank_max(staged_ms, group).mean())
+
+    # ---- end to end through the public API: pinned H2D, run, D2H, every step -----------------
+    idx_stage = torch.empty_like(idx_dev[0])
+    for s in range(args.warmup):
+        idx_stage.copy_(idx_pinned[s], non_blocking=True)
+        out_pinned.copy_(planner.run(idx_stage, avail, n_sms), non_blocking=True)
+        torch.cuda.synchronize(dev)
+    barrier()
+    t0 = time.perf_counter()
+    for k in range(args.steps):
+        idx_stage.copy_(idx_pinned[args.warmup + k], non_blocking=True)
+        out_pinned.copy_(planner.run(idx_stage, avail, n_sms), non_blocking=True)
+        torch.cuda.synchronize(dev)
+    e2e_ms = (time.perf_counter() - t0) * 1e3 / args.steps
+    e2e_ms = float(rank_max(torch.tensor([e2e_ms], dtype=torch.float64, device=dev), group)[0])
+    barrier()
+
+    value_us = ms_per_step * 1e3
+    result = {
+        "metric": METRIC,
+        "value": round(value_us, 3),
+        "unit": "us",
+        "n_gpus": world,
+        "steps": args.steps,
+        "warmup": args.warmup,
+        "ms_per_step": round(ms_per_step, 6),
+        "higher_is_better": False,
+        "scaling": "weak",
+        "vs_baseline": round(value_us / PUBLISHED_SOLVER_US, 4),
+        "dtype": "int64 indices, bf16 gate logits, fp64 LP",
+        "data": "synthetic",
+        "impl": "lplb_b200",
+        "config": {
+            "model": "DeepSeek-V3-shaped gate: 256 logical + 16 redundant experts, top-8",
+            "global_batch": TOKENS_PER_RANK * world,
+            "seq_len": 1,
+            "tokens_per_rank": TOKENS_PER_RANK,
+            "parallelism": f"ep8-cube LP over {world} rank(s)",
+            "comm": planner.comm,
+            "n_sms": n_sms,
+            "l2": "256 MiB buffer written between timed iterations",
+            "slow_path": "update_redundancy_mapping runs once before timing, not per step",
+        },
+        "clocks": clocks.summary(),
+        "e2e": {
+            "value": round(e2e_ms * 1e3, 3),
+            "unit": "us",
+            "h2d_bytes_per_step": idx_pinned[0].numel() * idx_pinned[0].element_size(),
+            "d2h_bytes_per_step": out_pinned.numel() * out_pinned.element_size(),
+        },
+        "gpu_launches": args.steps * (1 if planner.comm in ("p2p", "none") else 3),
+        "staged_nccl_pipeline_us": round(staged_ms * 1e3, 3),
+        "balance_max_over_mean": {"before": round(balance_before, 5), "after": round(balance_after, 5)},
+        "lp_iters_last": status["lp_iters"],
+        "status": status["error"],
+        "p50_us": round(float(per_step_ms.median()) * 1e3, 3),
+        "min_us": round(float(per_step_ms.min()) * 1e3, 3),
+    }
+    if group is not None:
+        import torch.distributed as dist
+
+        dist.destroy_process_group()
+    return result if rank == 0 else {}
+
+
+REFERENCE_DRIVER = r'''
+import json, os, sys, time
+sys.path.insert(0, os.path.join(ROOT, "baseline", "_ref"))
+sys.path.insert(0, ROOT)
+import torch
+import bench
+from lplb import Planner            # the unmodified reference
+args = bench.parse_args(ARGV)
+rank, world, local, group = bench.dist_setup(args.gpus)
+dev = torch.device("cuda", local)
+r2o = torch.tensor([[3, 0, 1, 2, 7, 4, 5, 6], [6, 7, 4, 5, 0, 1, 2, 3]]).T.int().cuda()
+planner = Planner(r2o, bench.N_LOGICAL + bench.RED_PER_RANK * bench.EP_SIZE, bench.N_LOGICAL, bench.EP_SIZE, group)
+n_sms = args.n_sms or torch.cuda.get_device_properties(dev).multi_processor_count
+total = args.warmup + args.steps
+idx = [bench.make_indices(s, rank, dev) for s in range(total)]
+hist = torch.zeros(bench.N_LOGICAL, dtype=torch.int64, device=dev)
+for s in range(min(8, total)):
+    hist += torch.bincount(idx[s].reshape(-1), minlength=bench.N_LOGICAL)
+if group is not None:
+    torch.distributed.all_reduce(hist, group=group)
+planner.update_redundancy_mapping(hist)
+avail = torch.zeros((), dtype=torch.int32, device=dev)
+flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
+for s in range(args.warmup):
+    planner.run(idx[s], avail, n_sms)
+starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+ends = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+torch.cuda.synchronize()
+with bench.ClockSampler(bench.physical_gpu_index(local)) as clocks:
+    for k in range(args.steps):
+        flush.fill_(k & 0xFF)
+        starts[k].record()
+        out = planner.run(idx[args.warmup + k], avail, n_sms)
+        ends[k].record()
+    torch.cuda.synchronize()
+ms = torch.tensor([a.elapsed_time(b) for a, b in zip(starts, ends)], dtype=torch.float64, device=dev)
+ms = float(bench.rank_max(ms, group).mean())
+if rank == 0:
+    print("REFERENCE_JSON " + json.dumps({
+        "impl": "reference", "metric": bench.METRIC, "value": round(ms * 1e3, 3), "unit": "us",
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
+        "higher_is_better": False, "scaling": "weak", "vs_baseline": round(ms * 1e3 / bench.PUBLISHED_SOLVER_US, 4),
+        "dtype": "int64 indices, fp32 LP", "data": "synthetic", "clocks": clocks.summary(),
+        "config": {"model": "DeepSeek-V3-shaped gate: 256 logical + 16 redundant experts, top-8",
+                   "global_batch": bench.TOKENS_PER_RANK * world, "seq_len": 1, "parallelism": "ep8-cube"}}))
+'''
+
+
+def run_reference(argv: list[str]) -> dict:
+    """Run the unmodified reference in a child process; report why if it cannot run."""
+    ref_dir = os.path.join(ROOT, "baseline", "_ref", "lplb")
+    if not os.path.isdir(ref_dir):
+        return {"impl": "reference", "unavailable": "baseline/_ref is not installed (offline pip install of the reference checkout was not done)"}
+    env = dict(os.environ)
+    env["LD_LIBRARY_PATH"] = "/usr/local/cuda/lib64:" + env.get("LD_LIBRARY_PATH", "")
+    env.setdefault("LPLB_CACHE_PATH", "/tmp/lplb_ref_cache")
+    code = f"ROOT = {ROOT!r}\nARGV = {argv!r}\n" + REFERENCE_DRIVER
+    try:
+        proc = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=900)
+    except subprocess.TimeoutExpired:
+        return {"impl": "reference", "unavailable": "reference run exceeded 900 s"}
+    for line in proc.stdout.splitlines():
+        if line.startswith("REFERENCE_JSON "):
+            return json.loads(line[len("REFERENCE_JSON "):])
+    tail = [ln.strip() for ln in (proc.stderr or proc.stdout).splitlines() if ln.strip()]
+    reason = tail[-1] if tail else f"exit code {proc.returncode}"
+    mathdx = os.path.isdir(os.path.join(ref_dir, "resources", "mathdx"))
+    note = "" if mathdx else " [lplb/resources/mathdx is absent: the kernels include cublasdx.hpp/cusolverdx.hpp, fetched by download-mathdx.sh from the network]"
+    return {"impl": "reference", "unavailable": (reason[:300] + note)}
+
+
+def parse_args(argv=None):
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--comm", choices=["auto", "p2p", "nccl", "none"], default="auto")
+    ap.add_argument("--n-sms", type=int, default=0, help="CTAs used by the planner kernels (default: all SMs)")
+    return ap.parse_args(argv)
+
+
+def main():
+    args = parse_args()
+    if args.warmup < 3:
+        args.warmup = 3
+    if args.impl == "reference":
+        result = run_reference(sys.argv[1:])
+        if int(os.environ.get("RANK", "0")) == 0:
+            print(json.dumps(result), flush=True)
+        return
+    result = run_ours(args)
+    if result:
+        print(json.dumps(result), flush=True)
+
+
+if __name__ == "__main__":
+    main()

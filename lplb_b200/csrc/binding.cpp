@@ -225,6 +225,45 @@ class PlannerEngine {
     exchange_open_ = true;
   }
 
+  // Single-process stand-in for the peer mapping, for tests on one GPU: every "peer"
+  // pointer aliases this rank's own block.  Slots and flags of the other ranks are only
+  // ever written by `debug_fill_slot`, so a test decides which peers "arrived".
+  void open_exchange_loopback(int n_ranks, int my_rank) {
+    LPLB_CHECK(!block_.base, "exchange buffers already allocated");
+    LPLB_CHECK(n_ranks >= 2 && n_ranks <= 32 && my_rank >= 0 && my_rank < n_ranks, "bad rank layout");
+    c10::cuda::CUDAGuard guard(device_);
+    n_ranks_ = n_ranks;
+    my_rank_ = my_rank;
+    recv_bytes_ = (sizeof(int) * 2 * (size_t)n_ranks * e_ + 255) / 256 * 256;
+    block_.bytes = recv_bytes_ + 256;
+    LPLB_CUDA(cudaMalloc(&block_.base, block_.bytes));
+    LPLB_CUDA(cudaMemset(block_.base, 0, block_.bytes));
+    std::vector<int64_t> recv(n_ranks_, reinterpret_cast<int64_t>(block_.base));
+    std::vector<int64_t> flags(n_ranks_, reinterpret_cast<int64_t>(static_cast<char*>(block_.base) + recv_bytes_));
+    auto opts = torch::TensorOptions().dtype(torch::kInt64);
+    recv_table_ = torch::from_blob(recv.data(), {n_ranks_}, opts).clone().to(torch::Device(torch::kCUDA, device_));
+    flag_table_ = torch::from_blob(flags.data(), {n_ranks_}, opts).clone().to(torch::Device(torch::kCUDA, device_));
+    peers_.clear();
+    exchange_open_ = true;
+  }
+
+  // Test hook: write `counts` into slot `rank` of both receive buffers and set that rank's
+  // arrival flag to `flag_value`.
+  void debug_fill_slot(int rank, const torch::Tensor& counts, int64_t flag_value) {
+    LPLB_CHECK(block_.base && rank >= 0 && rank < n_ranks_, "no exchange block or bad rank");
+    LPLB_CHECK(counts.numel() == e_, "counts must have E entries");
+    c10::cuda::CUDAGuard guard(device_);
+    auto host = counts.to(torch::kCPU, torch::kInt32).contiguous();
+    LPLB_CUDA(cudaDeviceSynchronize());
+    for (int parity = 0; parity < 2; ++parity) {
+      int* slot = static_cast<int*>(block_.base) + ((size_t)parity * n_ranks_ + rank) * e_;
+      LPLB_CUDA(cudaMemcpy(slot, host.data_ptr<int>(), sizeof(int) * e_, cudaMemcpyHostToDevice));
+    }
+    const uint32_t flag = (uint32_t)flag_value;
+    uint32_t* flags = reinterpret_cast<uint32_t*>(static_cast<char*>(block_.base) + recv_bytes_);
+    LPLB_CUDA(cudaMemcpy(flags + rank, &flag, sizeof(flag), cudaMemcpyHostToDevice));
+  }
+
   // Collective by convention: every rank calls it between steps, with no launch in flight,
   // after a barrier.  Zeroes this rank's epochs, flags and receive buffers.
   void reset_exchange() {
@@ -323,6 +362,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def("all_reduce_counts", &PlannerEngine::all_reduce_counts)
       .def("alloc_exchange", &PlannerEngine::alloc_exchange)
       .def("open_exchange", &PlannerEngine::open_exchange)
+      .def("open_exchange_loopback", &PlannerEngine::open_exchange_loopback)
+      .def("debug_fill_slot", &PlannerEngine::debug_fill_slot)
       .def("reset_exchange", &PlannerEngine::reset_exchange)
       .def("close_exchange", &PlannerEngine::close_exchange)
       .def("exchange_open", &PlannerEngine::exchange_open)

@@ -1,0 +1,290 @@
+"""Single-GPU tests of the native planner kernels against plain PyTorch references.
+
+Covers the reference's three test files (tests/test_solve.py, tests/test_idx_processing.py)
+through the same public API, plus small bounds cases, the fused single-launch path and
+the status block."""
+
+import pytest
+import torch
+
+from lplb_b200 import Planner, lp, topology
+from lplb_b200.ops import reference as ref
+from tests.helpers import SOLVE_CONFIGS, balance_after, synthetic_loads
+
+pytestmark = pytest.mark.gpu
+
+
+def _planner(r2o, n_logical, ep_size, n_red, **kw):
+    return Planner(r2o, n_logical + n_red * ep_size, n_logical, ep_size, device="cuda", **kw)
+
+
+def _sms():
+    return torch.cuda.get_device_properties(0).multi_processor_count
+
+
+# ---------------------------------------------------------------- histogram
+@pytest.mark.parametrize("dtype", [torch.int64, torch.int32])
+def test_count_workload_matches_scatter_add(dtype):
+    planner = _planner(topology.cube(), 256, 32, 2)
+    torch.manual_seed(42)
+    idx = torch.randint(-1, 256, (4096, 8), device="cuda").to(dtype)
+    counts, by_sm = planner.count_workload(idx, _sms())
+    assert counts.shape == (256,) and int(counts.min()) >= 0
+    assert int(counts.sum()) == int((idx != -1).sum())
+    want = torch.zeros(257, dtype=torch.long, device="cuda")
+    want.scatter_add_(0, idx.view(-1).long() + 1, torch.ones(idx.numel(), dtype=torch.long, device="cuda"))
+    assert torch.equal(counts.long(), want[1:])
+    ref_counts, ref_prefix = ref.count_reference(idx.cpu(), 256, _sms())
+    assert torch.equal(by_sm.cpu(), ref_prefix)
+
+
+@pytest.mark.parametrize("n_tokens,n_sms", [(0, 3), (1, 1), (255, 2), (257, 3), (5000, 7), (70000, 148), (300, 200)])
+def test_count_small_and_ragged_cases(n_tokens, n_sms):
+    planner = _planner(topology.cube(), 16, 8, 2)
+    idx = torch.randint(-1, 16, (n_tokens,), device="cuda", generator=torch.Generator("cuda").manual_seed(n_tokens))
+    counts, by_sm = planner.count_workload(idx, n_sms)
+    ref_counts, ref_prefix = ref.count_reference(idx.cpu(), 16, n_sms)
+    assert torch.equal(counts.cpu(), ref_counts) and torch.equal(by_sm.cpu(), ref_prefix)
+    # the kernel leaves its ticket at zero, so a second call gives the same answer
+    counts2, _ = planner.count_workload(idx, n_sms)
+    assert torch.equal(counts2, counts)
+
+
+def test_out_of_range_indices_are_counted_not_trapped():
+    planner = _planner(topology.cube(), 16, 8, 2)
+    idx = torch.tensor([0, 1, 16, 99, -1, -7, 3], device="cuda")
+    counts, _ = planner.count_workload(idx, 2)
+    assert counts.tolist() == [1, 1, 0, 1] + [0] * 12
+    st = planner.check_status(clear=True)
+    assert st["error"] == "bad_index" and st["bad_indices"] == 3
+    assert planner.check_status().ok
+
+
+# ---------------------------------------------------------------- LP
+@pytest.mark.parametrize("name,r2o,n_logical,ep_size,n_red,reorder,bound", SOLVE_CONFIGS)
+def test_planner_solve_quality(name, r2o, n_logical, ep_size, n_red, reorder, bound):
+    planner = _planner(r2o, n_logical, ep_size, n_red)
+    history, current = synthetic_loads(n_logical, seed=41, device="cuda")
+    phy2log, _, _ = planner.update_redundancy_mapping(history if reorder else None)
+    avail = torch.zeros((), dtype=torch.int32, device="cuda")
+    probs, normalised = planner.solve_probs(current, avail)
+    assert int(avail) == planner.n_group
+    assert probs.shape == (planner.n_group, planner.group_size, planner.num_redundants)
+    assert probs.dtype == torch.float32 and float(probs.min()) >= 0 and float(probs.max()) <= 1
+    assert torch.allclose(normalised.reshape(-1).cpu(), current.cpu().float() / float(current.max()))
+    assert balance_after(planner, phy2log, current, probs) < bound
+    # against the float64 oracle, group by group
+    w, fixed = lp.bundle_loads(
+        current.cpu().double(), phy2log.cpu(), planner.n_group, planner.group_size, planner.num_redundants,
+        planner.n_local_logical_routed_experts, planner.combined_redundant_experts,
+    )
+    realised = lp.rank_loads(probs.cpu().double(), w, fixed, r2o).max(-1).values
+    oracle = lp.solve_ipm(w, fixed, r2o, tol=1e-4)
+    assert float((probs.cpu().double() - oracle.f).abs().max()) < 1e-4
+    for grp in range(planner.n_group):
+        _, t_opt = lp.solve_highs(w[grp], fixed[grp], r2o)
+        assert (float(realised[grp]) - t_opt) / t_opt < 1e-3
+    st = planner.check_status()
+    assert st.ok and 1 <= st["lp_iters"] <= 12
+
+
+def test_solver_sweep_against_oracle():
+    # 512 Cube instances of the skewed shape: 128 experts, 16 per rank, Dirichlet(0.3)
+    import numpy as np
+
+    rng = np.random.default_rng(0)
+    n_group = 64
+    planner = _planner(topology.cube(), 128 * n_group, 8 * n_group, 2)
+    worst = 0.0
+    for _ in range(8):
+        cnt = np.stack([
+            -np.sort(-rng.multinomial(32768 * 8, rng.dirichlet(np.full(128, 0.3))).reshape(8, 16), axis=1)
+            for _ in range(n_group)
+        ])
+        current = torch.from_numpy(cnt.reshape(-1)).int().cuda()
+        avail = torch.zeros(1, dtype=torch.int64, device="cuda")
+        probs, _ = planner.solve_probs(current, avail)
+        assert int(avail) == n_group
+        w = torch.from_numpy(cnt[:, :, :2].astype(np.float64))
+        fixed = torch.from_numpy(cnt[:, :, 2:].sum(-1).astype(np.float64))
+        realised = lp.rank_loads(probs.cpu().double(), w, fixed, topology.cube()).max(-1).values
+        oracle = lp.solve_ipm(w, fixed, topology.cube(), tol=1e-9, max_iters=40)
+        gap = (realised - oracle.t) / oracle.t
+        worst = max(worst, float(gap.max()))
+        assert float(gap.min()) > -1e-7
+    assert worst < 1e-3
+
+
+def test_degenerate_loads_on_device():
+    planner = _planner(topology.cube(), 64 * 4, 32, 2)
+    current = torch.zeros(4, 8, 8, dtype=torch.int32)
+    current[1, 0, 0] = 1000
+    current[2, 3, 5] = 500
+    current[3] = 9
+    avail = torch.zeros((), dtype=torch.int32, device="cuda")
+    probs, normalised = planner.solve_probs(current.cuda().reshape(-1), avail)
+    assert int(avail) == 4 and not bool(torch.isnan(probs).any())
+    assert torch.equal(probs[0].cpu(), torch.ones(8, 2))
+    assert abs(float(probs[1, 0, 0]) - 0.5) < 1e-3
+    # all-zero input: nothing to normalise, nothing to balance, still no NaN
+    avail.zero_()
+    probs, normalised = planner.solve_probs(torch.zeros(256, dtype=torch.int32, device="cuda"), avail)
+    assert int(avail) == 4 and float(normalised.abs().max()) == 0 and float(probs.min()) == 1
+
+
+def test_iteration_cap_reports_failure():
+    planner = _planner(topology.cube(), 64, 8, 2, max_iters=1, tol=1e-9)
+    _, current = synthetic_loads(64, seed=1, device="cuda")
+    avail = torch.zeros((), dtype=torch.int32, device="cuda")
+    probs, _ = planner.solve_probs(current, avail)
+    assert int(avail) == 0
+    st = planner.check_status(clear=True)
+    assert st["error"] == "lp_not_converged" and st["lp_failures"] == 1
+    assert float(probs.min()) >= 0 and float(probs.max()) <= 1
+
+
+# ---------------------------------------------------------------- redirect
+def _check_redirect(planner, idx, out, probs):
+    m = planner.mapping
+    e, p = planner.n_logical_routed_experts, planner.n_routed_experts
+    idx_c, out_c = idx.reshape(-1).cpu().long(), out.reshape(-1).cpu().long()
+    assert out.shape == idx.shape and out.dtype == idx.dtype
+    assert int(out_c.min()) >= -1 and int(out_c.max()) < p
+    assert torch.equal(out_c == -1, idx_c == -1)
+    padded = torch.cat([torch.full((1, 2), -1, dtype=torch.int32), m.log2phy.cpu()]).long()
+    orig, repl = padded[idx_c + 1, 0], padded[idx_c + 1, 1]
+    assert bool(((out_c == orig) | (out_c == repl)).all())
+    valid = idx_c >= 0
+    total = torch.bincount(idx_c[valid], minlength=e)
+    kept = torch.bincount(idx_c[valid & (out_c == orig)], minlength=e)
+    quota = ref.quotas_reference(total, probs.cpu(), m.log2edge.cpu())
+    assert torch.equal(kept, quota)
+
+
+def test_weighted_select_target_exact_quotas():
+    planner = _planner(topology.cube(), 256, 32, 2)
+    torch.manual_seed(42)
+    history = (torch.randn(256, device="cuda") * 0.15 + 1).clamp_min(0).mul(2**20).long()
+    planner.update_redundancy_mapping(history)
+    idx = torch.randint(-1, 256, (65536,), device="cuda")
+    o_weight = (torch.randn(4, 8, 2, device="cuda") / 3 + 0.5).clamp(0, 1)
+    _, by_sm = planner.count_workload(idx, _sms())
+    out = planner.weighted_select_target(idx, o_weight, by_sm, _sms())
+    _check_redirect(planner, idx, out, o_weight)
+    # realised share vs requested share, the reference's 5e-2 criterion
+    # (reference tests/test_idx_processing.py:132-138)
+    m = planner.mapping
+    rep = m.log2edge.cpu().long() >= 0
+    idx_c, out_c = idx.cpu(), out.cpu()
+    total = torch.bincount(idx_c[idx_c >= 0], minlength=256)[rep].double()
+    kept = torch.bincount(idx_c[(idx_c >= 0) & (out_c == m.log2phy.cpu().long()[idx_c.clamp_min(0), 0])], minlength=256)[rep].double()
+    want = o_weight.reshape(-1).cpu().double()[m.log2edge.cpu().long()[rep]]
+    assert float((kept / total - want).abs().max()) < 5e-2
+
+
+@pytest.mark.parametrize("n_tokens,n_sms,quota", [(1, 1, 0.5), (499 * 4, 3, 0.37), (1000, 5, 0.0), (1000, 5, 1.0), (70000, 148, 0.123)])
+def test_redirect_degenerate_quotas(n_tokens, n_sms, quota):
+    # includes totals that are multiples of 499, where the reference's hash degenerates
+    planner = _planner(topology.cube(), 16, 8, 2)
+    idx = torch.randint(0, 2, (n_tokens,), device="cuda") * 0  # every token picks expert 0
+    probs = torch.full((1, 8, 2), quota, device="cuda")
+    _, by_sm = planner.count_workload(idx, n_sms)
+    out = planner.weighted_select_target(idx, probs, by_sm, n_sms)
+    _check_redirect(planner, idx, out, probs)
+
+
+# ---------------------------------------------------------------- fused run
+@pytest.mark.parametrize("name,r2o,n_logical,ep_size,n_red", [
+    ("cube", topology.cube(), 256, 8, 2),
+    ("cube-ep32", topology.cube(), 256, 32, 2),
+    ("ring", topology.ring(8), 64, 8, 1),
+    ("hypercube", topology.hypercube(), 256, 16, 2),
+    ("torus2x4", topology.torus(2, 4), 512, 8, 2),
+    ("torus8x4-c2", topology.torus(8, 4), 256, 32, 4),
+])
+def test_fused_run_matches_staged_pipeline(name, r2o, n_logical, ep_size, n_red):
+    planner = _planner(r2o, n_logical, ep_size, n_red)
+    gen = torch.Generator("cuda").manual_seed(5)
+    for step, n_sms in enumerate([_sms(), 13, 1, _sms()]):
+        bias = torch.randn(n_logical, device="cuda", generator=gen)
+        logits = torch.randn(2048, n_logical, device="cuda", generator=gen) + bias
+        idx = logits.topk(8, dim=-1).indices
+        if step == 1:
+            planner.update_redundancy_mapping(torch.bincount(idx.reshape(-1), minlength=n_logical))
+            idx[::7, 3] = -1
+        avail = torch.zeros((), dtype=torch.int32, device="cuda")
+        out = planner.run(idx, avail, n_sms)
+        assert int(avail) == planner.n_group
+        probs = planner.last_probs.clone()
+        _check_redirect(planner, idx, out, probs)
+        avail2 = torch.zeros((), dtype=torch.int32, device="cuda")
+        counts, _ = planner.count_workload(idx, n_sms)
+        staged_probs, _ = planner.solve_probs(counts, avail2)
+        assert torch.equal(staged_probs, probs)  # same arithmetic on the same counts
+        assert planner.check_status().ok
+    assert planner.check_status()["calls"] == 4
+
+
+def test_fused_run_balances_real_routing():
+    planner = _planner(topology.cube(), 256, 8, 2)
+    gen = torch.Generator("cuda").manual_seed(0)
+    bias = torch.randn(256, device="cuda", generator=gen)
+    logits = (torch.randn(4096, 256, device="cuda", generator=gen) + bias).bfloat16()
+    idx = logits.topk(8, dim=-1).indices
+    planner.update_redundancy_mapping(torch.bincount(idx.reshape(-1), minlength=256))
+    avail = torch.zeros(1, dtype=torch.int64, device="cuda")
+    out = planner.run(idx, avail)
+    assert int(avail) == 1
+    pl = planner.n_local_routed_experts
+    before = torch.bincount(planner.mapping.log2phy[idx.reshape(-1), 0].long() // pl, minlength=8).double()
+    after = torch.bincount(out.reshape(-1) // pl, minlength=8).double()
+    assert float(after.max() / after.mean()) < float(before.max() / before.mean())
+    # the realised max load is the LP optimum up to rounding of quotas
+    counts = torch.bincount(idx.reshape(-1), minlength=256)
+    w, fixed = lp.bundle_loads(counts.cpu().double(), planner.phy2log.cpu(), 1, 8, 2, 32, 1)
+    _, t_opt = lp.solve_highs(w[0], fixed[0], topology.cube())
+    assert float(after.max()) <= t_opt * (1 + 1e-3) + 16
+
+
+# ---------------------------------------------------------------- exchange on one GPU
+def test_exchange_loopback_sums_prefilled_peer():
+    planner = _planner(topology.cube(), 64, 8, 2)
+    eng = planner._engine
+    eng.open_exchange_loopback(2, 0)
+    peer = torch.arange(64, dtype=torch.int32) * 3
+    eng.debug_fill_slot(1, peer, 0x3FFFFFFF)  # "rank 1 arrived for every epoch to come"
+    mine = torch.randint(0, 100, (64,), dtype=torch.int32, device="cuda")
+    for _ in range(3):  # both parities
+        got = eng.all_reduce_counts(mine)
+        assert torch.equal(got.cpu(), mine.cpu() + peer)
+    idx = torch.randint(0, 64, (4096, 4), device="cuda")
+    avail = torch.zeros((), dtype=torch.int32, device="cuda")
+    out = eng.run_fused(idx, avail, 16, True)
+    counts = torch.bincount(idx.reshape(-1), minlength=64).int()
+    ws = eng.workspace()
+    glob = ws[8 + 2 * 64 : 8 + 3 * 64]
+    assert torch.equal(glob.cpu(), counts.cpu() + peer)
+    assert planner.check_status().ok
+    _check_redirect(planner, idx, out, eng.last_probs())
+
+
+def test_exchange_wait_runs_out_and_falls_back():
+    # a flag that nothing sets: the wait must end by itself, report, and still route
+    planner = _planner(topology.cube(), 64, 8, 2, peer_timeout_us=300.0)
+    eng = planner._engine
+    eng.open_exchange_loopback(2, 0)
+    idx = torch.randint(0, 64, (4096, 4), device="cuda")
+    avail = torch.zeros((), dtype=torch.int32, device="cuda")
+    out = eng.run_fused(idx, avail, 8, True)
+    torch.cuda.synchronize()
+    st = planner.check_status(clear=True)
+    assert st["error"] == "peer_timeout" and st["phase"] == "exchange" and st["detail"] == 0b10 and st["timeouts"] == 1
+    assert int(avail) == 1
+    _check_redirect(planner, idx, out, eng.last_probs())
+    # fallback used this rank's counts for the absent peer: shares equal the local solve
+    local = Planner(topology.cube(), 80, 64, 8, device="cuda")
+    a2 = torch.zeros((), dtype=torch.int32, device="cuda")
+    local.run(idx, a2, 8)
+    assert torch.allclose(local.last_probs, eng.last_probs(), atol=1e-6)
+    # the context is still healthy
+    assert int(torch.ones(4, device="cuda").sum()) == 4
