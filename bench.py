@@ -210,6 +210,22 @@ def run_ours(args) -> dict:
     per_step_ms = rank_max(per_step_ms, group)
     ms_per_step = float(per_step_ms.mean())
     status = planner.check_status()
+    if args.dump and rank == 0:
+        os.makedirs(os.path.dirname(os.path.abspath(args.dump)), exist_ok=True)
+        with open(args.dump, "w") as fh:
+            fh.write("\n".join(f"{v * 1e3:.3f}" for v in per_step_ms.tolist()))
+
+    # LP optimum of the last step's global statistics (float64 HiGHS) for the quality claim
+    counts = torch.bincount(idx_dev[-1].reshape(-1), minlength=N_LOGICAL)
+    if group is not None:
+        import torch.distributed as dist
+
+        dist.all_reduce(counts, group=group)
+    from lplb_b200 import lp as _lp
+
+    w_b, f_b = _lp.bundle_loads(counts.cpu().double(), planner.phy2log.cpu(), 1, EP_SIZE, RED_PER_RANK, N_LOGICAL // EP_SIZE, 1)
+    _, t_opt = _lp.solve_highs(w_b[0], f_b[0], cube())
+    optimum_ratio = t_opt / float(counts.sum() / EP_SIZE)
     balance_after = post_balance(planner, out, group, pl)
     naive = planner.mapping.log2phy[idx_dev[-1].reshape(-1), 0].long()
     balance_before = post_balance(planner, naive, group, pl)
@@ -283,12 +299,29 @@ def run_ours(args) -> dict:
         },
         "gpu_launches": args.steps * (1 if planner.comm in ("p2p", "none") else 3),
         "staged_nccl_pipeline_us": round(staged_ms * 1e3, 3),
-        "balance_max_over_mean": {"before": round(balance_before, 5), "after": round(balance_after, 5)},
+        "balance_max_over_mean": {
+            "before": round(balance_before, 5),
+            "after": round(balance_after, 5),
+            "lp_optimum_float64": round(optimum_ratio, 5),
+        },
         "lp_iters_last": status["lp_iters"],
         "status": status["error"],
         "p50_us": round(float(per_step_ms.median()) * 1e3, 3),
+        "p90_us": round(float(per_step_ms.quantile(0.9)) * 1e3, 3),
+        "max_us": round(float(per_step_ms.max()) * 1e3, 3),
         "min_us": round(float(per_step_ms.min()) * 1e3, 3),
     }
+    if args.trace:
+        planner.enable_trace(True)
+        rows = []
+        for k in range(min(args.steps, 50)):
+            flush.fill_(k & 0xFF)
+            planner.run(idx_dev[args.warmup + k], avail, n_sms)
+            rows.append(planner.phase_times_us())
+        planner.enable_trace(False)
+        result["phases_us_median"] = {
+            key: round(statistics.median(r[key] for r in rows), 2) for key in rows[0]
+        }
     if group is not None:
         import torch.distributed as dist
 
@@ -375,6 +408,8 @@ def parse_args(argv=None):
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--comm", choices=["auto", "p2p", "nccl", "none"], default="auto")
     ap.add_argument("--n-sms", type=int, default=0, help="CTAs used by the planner kernels (default: all SMs)")
+    ap.add_argument("--trace", action="store_true", help="add per-phase device times from the kernel's own stamps")
+    ap.add_argument("--dump", default="", help="write the per-step device times (us) to this file")
     return ap.parse_args(argv)
 
 

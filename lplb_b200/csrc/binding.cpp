@@ -177,7 +177,9 @@ class PlannerEngine {
     }
     LPLB_CUDA(lplb::launch_fused(idx.data_ptr(), is64, idx.numel(), topo(), ex, prm_, workspace_.data_ptr(),
                                  probs_.data_ptr<float>(), avail.data_ptr(), avail.scalar_type() == torch::kInt64,
-                                 status_.data_ptr<int>(), out.data_ptr(), n_cta, grid_timeout_ns_, stream()));
+                                 status_.data_ptr<int>(), out.data_ptr(), n_cta, grid_timeout_ns_,
+                                 trace_.defined() ? reinterpret_cast<unsigned long long*>(trace_.data_ptr()) : nullptr,
+                                 cooperative_ ? 1 : 0, stream()));
     return out;
   }
 
@@ -286,6 +288,19 @@ class PlannerEngine {
     exchange_open_ = false;
   }
 
+  // Cooperative launch (default) makes the driver guarantee that all CTAs of the fused kernel
+  // are co-resident; an ordinary launch is cheaper but leaves that to the caller.
+  void set_cooperative(bool on) { cooperative_ = on; }
+
+  // Phase stamps of the fused kernel (see fused_run_kernel): off by default.
+  void enable_trace(bool on) {
+    c10::cuda::CUDAGuard guard(device_);
+    if (on && !trace_.defined())
+      trace_ = torch::zeros({8}, torch::TensorOptions().dtype(torch::kInt64).device(torch::kCUDA, device_));
+    if (!on) trace_ = torch::Tensor();
+  }
+  torch::Tensor trace() const { return trace_; }
+
   bool exchange_open() const { return exchange_open_; }
   torch::Tensor status() const { return status_; }
   torch::Tensor last_probs() const { return probs_; }
@@ -334,7 +349,7 @@ class PlannerEngine {
   lplb::SolveParams prm_{24, 1e-4};
   unsigned long long peer_timeout_ns_ = 1000000000ull, grid_timeout_ns_ = 1000000000ull;
   torch::Tensor r2o_, o2r_, phy2log_, log2phy_, log2edge_;
-  torch::Tensor workspace_, status_, probs_;
+  torch::Tensor workspace_, status_, probs_, trace_;
   int max_cta64_ = -1, max_cta32_ = -1;
   // exchange
   IpcBlock block_;
@@ -343,6 +358,7 @@ class PlannerEngine {
   torch::Tensor recv_table_, flag_table_;
   int n_ranks_ = 1, my_rank_ = 0;
   bool exchange_open_ = false;
+  bool cooperative_ = true;
 };
 
 }  // namespace
@@ -367,6 +383,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def("reset_exchange", &PlannerEngine::reset_exchange)
       .def("close_exchange", &PlannerEngine::close_exchange)
       .def("exchange_open", &PlannerEngine::exchange_open)
+      .def("set_cooperative", &PlannerEngine::set_cooperative)
+      .def("enable_trace", &PlannerEngine::enable_trace)
+      .def("trace", &PlannerEngine::trace)
       .def("status", &PlannerEngine::status)
       .def("last_probs", &PlannerEngine::last_probs)
       .def("workspace", &PlannerEngine::workspace)

@@ -10,10 +10,11 @@
 //
 // The method is a Mehrotra predictor-corrector primal-dual iteration in float64 on the
 // compact form.  The normal matrix N = M diag(theta) M^T + diag(s/y) is a weighted
-// graph Laplacian of the topology plus a positive diagonal, GP x GP.  Lane i keeps row i
-// in registers; the Cholesky factorisation updates both triangles so that after step j
-// lane j already holds column j of L, which lets forward and backward substitution run
-// with statically indexed registers.
+// graph Laplacian of the topology plus a positive diagonal, GP x GP, factored as L D L^T
+// (no square roots).  For GP = 16 and 32 lane i keeps row i in registers and the
+// factorisation updates both triangles, so that after step j lane j already holds column j
+// of L and both substitutions run with statically indexed registers.  For GP = 8 the 36
+// entries are all-gathered and every lane factors and solves the whole system itself.
 //
 // It replaces the reference's primal affine-scaling loop on the (G+GD) x (2GD+G+2)
 // equality form with cuBLASDx/cuSolverDx block calls
@@ -73,33 +74,120 @@ __device__ __forceinline__ float ratio_to_bound(double val, double dval) {
   return dval < 0.0 ? __fdividef((float)val, -(float)dval) : 3.0e38f;
 }
 
-// Solve L L^T x = g for two right-hand sides held one element per lane.  `row` is the
-// factor as left by the factorisation in ipm_solve_segment: on lane i, row[j<i] = L[i][j],
-// row[i] = 1/L[i][i], row[j>i] = L[j][i].
+// 1/x for a positive, finite double: the hardware's ~2^-23 approximation refined by two
+// Newton steps (error squared each time), five dependent instructions instead of the
+// forty-odd of an IEEE division.  Relative error is a few ulp, far below the solver's needs.
+__device__ __forceinline__ double fast_rcp(double x) {
+#ifdef LPLB_HOST_SIM
+  return 1.0 / x;
+#else
+  double r;
+  asm("rcp.approx.ftz.f64 %0, %1;" : "=d"(r) : "d"(x));
+  r = fma(r, fma(-x, r, 1.0), r);
+  r = fma(r, fma(-x, r, 1.0), r);
+  return r;
+#endif
+}
+
+// ---- distributed factorisation (any GP): lane i keeps row i ---------------------------------
+// N = L D L^T with unit lower L.  Both triangles of the trailing matrix are kept current, so
+// after step j lane j can read column j of L out of its own row by symmetry.  On return, on
+// lane i: row[j<i] = L[i][j], row[i] = 1/D[i], row[j>i] = L[j][i].  A pivot that rounding
+// drove non-positive or non-finite is replaced by a huge one, which zeroes that unknown in
+// the solves instead of spreading NaNs.  Updates are masked multiplies, not branches.
 template <int GP>
-__device__ __forceinline__ void chol_solve2(const double (&row)[GP], int li, double& g0, double& g1) {
+__device__ __forceinline__ void ldl_factor_rows(double (&row)[GP], int li) {
 #pragma unroll
   for (int j = 0; j < GP; ++j) {
-    const double x0 = seg_shfl<GP>(g0 * row[j], j), x1 = seg_shfl<GP>(g1 * row[j], j);
-    if (li > j) {
-      g0 -= row[j] * x0;
-      g1 -= row[j] * x1;
-    } else if (li == j) {
-      g0 = x0;
-      g1 = x1;
+    double piv = seg_shfl<GP>(row[j], j);
+    if (!(piv > 1e-300) || !(piv < 1e300)) piv = 1e300;
+    const double dinv = fast_rcp(piv);
+    const double lij = li > j ? row[j] * dinv : 0.0;  // L[i][j] on lanes below the pivot, else 0
+#pragma unroll
+    for (int k = j + 1; k < GP; ++k) {
+      const double u = seg_shfl<GP>(row[k], j);  // unscaled N[j][k] = N[k][j]
+      row[k] = fma(-lij, u, row[k]);
+      if (li == j) row[k] = u * dinv;            // lane j keeps L[k][j] for the backward sweep
     }
+    row[j] = li > j ? lij : (li == j ? dinv : row[j]);
+  }
+}
+
+// Solve L D L^T x = g for two right-hand sides held one element per lane.
+template <int GP>
+__device__ __forceinline__ void ldl_solve2_rows(const double (&row)[GP], int li, double& g0, double& g1) {
+#pragma unroll
+  for (int j = 0; j < GP; ++j) {
+    const double x0 = seg_shfl<GP>(g0, j), x1 = seg_shfl<GP>(g1, j);
+    const double l = li > j ? row[j] : 0.0;
+    g0 = fma(-l, x0, g0);
+    g1 = fma(-l, x1, g1);
+  }
+  {
+    double dinv = row[0];
+#pragma unroll
+    for (int j = 1; j < GP; ++j) dinv = li == j ? row[j] : dinv;
+    g0 *= dinv;
+    g1 *= dinv;
   }
 #pragma unroll
   for (int j = GP - 1; j >= 0; --j) {
-    const double x0 = seg_shfl<GP>(g0 * row[j], j), x1 = seg_shfl<GP>(g1 * row[j], j);
-    if (li < j) {
-      g0 -= row[j] * x0;
-      g1 -= row[j] * x1;
-    } else if (li == j) {
-      g0 = x0;
-      g1 = x1;
-    }
+    const double x0 = seg_shfl<GP>(g0, j), x1 = seg_shfl<GP>(g1, j);
+    const double l = li < j ? row[j] : 0.0;
+    g0 = fma(-l, x0, g0);
+    g1 = fma(-l, x1, g1);
   }
+}
+
+// ---- replicated factorisation (GP == 8): every lane factors the whole 8x8 matrix -----------
+// The 36 entries of the lower triangle are all-gathered with shuffles, after which the
+// factorisation and the substitutions are straight-line FMA code with static register
+// indices: no shuffle latency on the dependent chain, no predication.
+struct Ldl8 {
+  double a[36];    // lower triangle, row-major packed: (i, k) at i*(i+1)/2 + k; L below, unused on the diagonal
+  double dinv[8];  // 1/D
+  __device__ __forceinline__ static constexpr int at(int i, int k) { return i * (i + 1) / 2 + k; }
+};
+
+__device__ __forceinline__ void ldl8_factor(const double (&row)[8], Ldl8& m) {
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+#pragma unroll
+    for (int k = 0; k <= i; ++k) m.a[Ldl8::at(i, k)] = seg_shfl<8>(row[k], i);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    double piv = m.a[Ldl8::at(j, j)];
+    if (!(piv > 1e-300) || !(piv < 1e300)) piv = 1e300;
+    m.dinv[j] = fast_rcp(piv);
+#pragma unroll
+    for (int i = j + 1; i < 8; ++i) {
+      const double lij = m.a[Ldl8::at(i, j)] * m.dinv[j];
+#pragma unroll
+      for (int k = j + 1; k <= i; ++k) m.a[Ldl8::at(i, k)] = fma(-lij, m.a[Ldl8::at(k, j)], m.a[Ldl8::at(i, k)]);
+    }
+#pragma unroll
+    for (int i = j + 1; i < 8; ++i) m.a[Ldl8::at(i, j)] *= m.dinv[j];
+  }
+}
+
+__device__ __forceinline__ double ldl8_solve(const Ldl8& m, int li, double g) {
+  double b[8];
+#pragma unroll
+  for (int k = 0; k < 8; ++k) b[k] = seg_shfl<8>(g, k);
+#pragma unroll
+  for (int j = 0; j < 8; ++j)
+#pragma unroll
+    for (int i = j + 1; i < 8; ++i) b[i] = fma(-m.a[Ldl8::at(i, j)], b[j], b[i]);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) b[j] *= m.dinv[j];
+#pragma unroll
+  for (int j = 7; j >= 0; --j)
+#pragma unroll
+    for (int i = 0; i < j; ++i) b[i] = fma(-m.a[Ldl8::at(j, i)], b[j], b[i]);
+  double x = b[0];
+#pragma unroll
+  for (int k = 1; k < 8; ++k) x = li == k ? b[k] : x;
+  return x;
 }
 
 // All 32 lanes must call this together.  `li` is the lane's index inside its segment.
@@ -165,7 +253,7 @@ __device__ IpmOutcome ipm_solve_segment(int li, const double (&w_in)[D], double 
 
   bool done = empty;
   int iters = 0;
-  double gap = 1e300;
+  double gap = 1e300, gap_scale = 1.0;
 
   for (int it = 0; it <= prm.max_iters; ++it) {
     // ---- residuals, gap, stopping test ---------------------------------------------
@@ -188,8 +276,9 @@ __device__ IpmOutcome ipm_solve_segment(int li, const double (&w_in)[D], double 
     const double dual = seg_sum<GP>(dual_part + neg_rd);
     const double infeas = fmax(seg_max<GP>(worst_u), fabs(r_t));
     if (!done) {
-      gap = (primal - dual) / fmax(fabs(primal), 1e-300);
-      if (gap <= prm.tol && infeas <= prm.tol) done = true;
+      gap = primal - dual;  // absolute here, made relative once at the end
+      gap_scale = fabs(primal);
+      if (gap <= prm.tol * gap_scale && infeas <= prm.tol) done = true;
     }
     // Every segment of the warp has to leave the loop together.
     if (__all_sync(0xffffffffu, done) || it == prm.max_iters) break;
@@ -197,12 +286,13 @@ __device__ IpmOutcome ipm_solve_segment(int li, const double (&w_in)[D], double 
 
     // ---- normal matrix row -----------------------------------------------------------
     double inv_f[D], inv_v[D], theta[D], cw[D];
-    const double inv_y = 1.0 / y;
+    const double inv_y = fast_rcp(y);
+    const double inv_mu = fast_rcp(kComp * mu);
 #pragma unroll
     for (int d = 0; d < D; ++d) {
-      inv_f[d] = 1.0 / f[d];
-      inv_v[d] = 1.0 / v[d];
-      theta[d] = 1.0 / (z[d] * inv_f[d] + q[d] * inv_v[d]);
+      inv_f[d] = fast_rcp(f[d]);
+      inv_v[d] = fast_rcp(v[d]);
+      theta[d] = fast_rcp(z[d] * inv_f[d] + q[d] * inv_v[d]);
       cw[d] = theta[d] * w[d] * w[d];
     }
     double row[GP];
@@ -226,32 +316,16 @@ __device__ IpmOutcome ipm_solve_segment(int li, const double (&w_in)[D], double 
       }
     }
 
-    // ---- Cholesky, both triangles kept current -------------------------------------------
-    // afterwards on lane i: row[j<i] = L[i][j], row[i] = 1/L[i][i], row[j>i] = L[j][i]
-#pragma unroll
-    for (int j = 0; j < GP; ++j) {
-      double piv = seg_shfl<GP>(row[j], j);
-      if (!(piv > 1e-300) || !(piv < 1e300)) piv = 1e300;  // drop a dead pivot instead of emitting NaN
-      const double rinv = rsqrt(piv);
-      if (li == j) {
-#pragma unroll
-        for (int k = j + 1; k < GP; ++k) row[k] *= rinv;
-        row[j] = rinv;
-      }
-      const double lij = row[j] * rinv;  // meaningful on lanes > j
-#pragma unroll
-      for (int k = j + 1; k < GP; ++k) {
-        const double lk = seg_shfl<GP>(row[k], j);
-        if (li > j) row[k] -= lij * lk;
-      }
-      if (li > j) row[j] = lij;
-    }
+    // ---- factorisation -------------------------------------------------------------------
+    Ldl8 dense;
+    if constexpr (GP == 8) ldl8_factor(row, dense);
+    else ldl_factor_rows<GP>(row, li);
 
     // ---- predictor (pass 0) and corrector (pass 1) share one body ------------------------
     // Pass 0 also solves N b = 1 for the border column that carries sum(dy) = r_t; pass 1
     // sends a dummy second right-hand side through the same substitution code.
     double df[D], dv[D], dz[D], dq[D], ds = 0.0, dy = 0.0, dt = 0.0;
-    double border = 1.0, border_sum = 1.0, sm = 0.0;
+    double border = 1.0, inv_border_sum = 1.0, sm = 0.0;
 #pragma unroll
     for (int d = 0; d < D; ++d) df[d] = dv[d] = dz[d] = dq[d] = 0.0;
     float apf = 0.f, adf = 0.f;
@@ -270,13 +344,16 @@ __device__ IpmOutcome ipm_solve_segment(int li, const double (&w_in)[D], double 
         acc += wx - seg_shfl<GP>(wx, src[d]);
       }
       double a = acc - r_p + r_sy * inv_y;
-      double b2 = pass == 0 ? 1.0 : 0.0;
-      chol_solve2<GP>(row, li, a, b2);
-      if (pass == 0) {
-        border = b2;
-        border_sum = seg_sum<GP>(border);
+      if constexpr (GP == 8) {
+        a = ldl8_solve(dense, li, a);
+        if (pass == 0) border = ldl8_solve(dense, li, 1.0);
+      } else {
+        double b2 = pass == 0 ? 1.0 : 0.0;
+        ldl_solve2_rows<GP>(row, li, a, b2);
+        if (pass == 0) border = b2;
       }
-      dt = (seg_sum<GP>(a) - r_t) / border_sum;
+      if (pass == 0) inv_border_sum = fast_rcp(seg_sum<GP>(border));
+      dt = (seg_sum<GP>(a) - r_t) * inv_border_sum;
       dy = a - dt * border;
       ds = (r_sy - s * dy) * inv_y;
       float rp = ratio_to_bound(s, ds), rd = ratio_to_bound(y, dy);
@@ -297,7 +374,7 @@ __device__ IpmOutcome ipm_solve_segment(int li, const double (&w_in)[D], double 
 #pragma unroll
         for (int d = 0; d < D; ++d)
           comp_aff += (z[d] + ad * dz[d]) * (f[d] + ap * df[d]) + (q[d] + ad * dq[d]) * (v[d] + ap * dv[d]);
-        const double ratio = fmin(fmax(seg_sum<GP>(comp_aff) / (kComp * mu), 0.0), 1.0);
+        const double ratio = fmin(fmax(seg_sum<GP>(comp_aff) * inv_mu, 0.0), 1.0);
         sm = ratio * ratio * ratio * mu;
       }
     }
@@ -335,7 +412,7 @@ __device__ IpmOutcome ipm_solve_segment(int li, const double (&w_in)[D], double 
   out.iters = iters;
   out.converged = done && finite;
   out.finite = finite;
-  out.gap = gap;
+  out.gap = empty ? 0.0 : gap / fmax(gap_scale, 1e-300);
   return out;
 }
 

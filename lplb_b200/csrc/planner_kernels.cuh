@@ -341,9 +341,15 @@ template <int GP, int D, typename IdxT>
 __global__ void __launch_bounds__(kBlock) fused_run_kernel(const IdxT* __restrict__ idx, long long n, Topo tp,
                                                            Exchange ex, IpmParams prm, Workspace* ws,
                                                            float* __restrict__ probs, Counter avail, int* status,
-                                                           IdxT* __restrict__ out, unsigned long long grid_timeout_ns) {
+                                                           IdxT* __restrict__ out, unsigned long long grid_timeout_ns,
+                                                           unsigned long long* __restrict__ trace) {
   extern __shared__ int smem[];
   const int e = tp.e, p = blockIdx.x, n_cta = gridDim.x;
+  // Optional phase stamps (globaltimer, ns) written by thread 0 of CTA 0 and by the CTA
+  // that leaves last: 0 start, 1 own slice counted, 2 all CTAs arrived, 3 statistics
+  // exchanged, 4 LPs solved, 5 CTA 0 redirected its slice, 6 last CTA left.
+  const bool tracing = trace != nullptr && threadIdx.x == 0;
+  if (tracing && p == 0) trace[0] = global_timer_ns();
   int* hist = smem;        // this CTA's counts, later the rank-local totals
   int* cur = hist + e;     // next ordinal to hand out per expert
   int* quota = cur + e;
@@ -370,8 +376,10 @@ __global__ void __launch_bounds__(kBlock) fused_run_kernel(const IdxT* __restric
   if (threadIdx.x == 0) atomicAdd(&ws->arrive, 1u);
 
   if (p == 0) {
+    if (tracing) trace[1] = global_timer_ns();
     if (threadIdx.x == 0) {
       s_ok = bounded_wait_ge<false>(&ws->arrive, (uint32_t)n_cta, grid_timeout_ns);
+      if (tracing) trace[2] = global_timer_ns();
       if (!s_ok) {
         atomicAdd(&status[kStTimeouts], 1);
         raise_status(status, kErrGridTimeout, kPhCount, (int)ld_acquire_gpu(&ws->arrive));
@@ -399,10 +407,12 @@ __global__ void __launch_bounds__(kBlock) fused_run_kernel(const IdxT* __restric
     }
     int* glob = ws_global(ws, e);
     for (int i = threadIdx.x; i < e; i += kBlock) glob[i] = summed[i];
+    if (tracing) trace[3] = global_timer_ns();
     solve_groups<GP, D>(summed, tp, 0, kWarps * (32 / GP), prm, probs, avail, status);
     __threadfence();
     __syncthreads();
     if (threadIdx.x == 0) st_release_gpu(&ws->lp_done, epoch);
+    if (tracing) trace[4] = global_timer_ns();
   }
 
   if (threadIdx.x == 0) {
@@ -425,6 +435,7 @@ __global__ void __launch_bounds__(kBlock) fused_run_kernel(const IdxT* __restric
   redirect_slice(idx, begin, end, e, cur, hist, quota, phys, out);
 
   __syncthreads();
+  if (tracing && p == 0) trace[5] = global_timer_ns();
   if (threadIdx.x == 0) {
     __threadfence();
     if (atomicAdd(&ws->exit_cnt, 1u) == (unsigned)n_cta - 1) {
@@ -432,6 +443,7 @@ __global__ void __launch_bounds__(kBlock) fused_run_kernel(const IdxT* __restric
       ws->exit_cnt = 0;
       atomicAdd(&status[kStCalls], 1);
       st_release_gpu(&ws->epoch, epoch);
+      if (trace != nullptr) trace[6] = global_timer_ns();
     }
   }
 }

@@ -138,6 +138,8 @@ struct FusedLaunch {
   IdxT* out;
   int n_cta;
   unsigned long long grid_timeout_ns;
+  unsigned long long* trace;
+  int cooperative;
   cudaStream_t stream;
   template <int GP, int D>
   cudaError_t operator()() {
@@ -145,27 +147,31 @@ struct FusedLaunch {
     const size_t smem = fused_smem(tp.e);
     cudaError_t err = allow_smem(kernel, smem);
     if (err != cudaSuccess) return err;
-    void* args[] = {&idx, &n, &tp, &ex, &prm, &ws, &probs, &avail, &status, &out, &grid_timeout_ns};
-    return cudaLaunchCooperativeKernel(reinterpret_cast<void*>(kernel), dim3(n_cta), dim3(kBlock), args, smem, stream);
+    void* args[] = {&idx, &n, &tp, &ex, &prm, &ws, &probs, &avail, &status, &out, &grid_timeout_ns, &trace};
+    if (cooperative)
+      return cudaLaunchCooperativeKernel(reinterpret_cast<void*>(kernel), dim3(n_cta), dim3(kBlock), args, smem,
+                                         stream);
+    return cudaLaunchKernel(reinterpret_cast<void*>(kernel), dim3(n_cta), dim3(kBlock), args, smem, stream);
   }
 };
 
 cudaError_t launch_fused(const void* idx, int idx_is64, long long n, const TopoDesc& topo, const ExchangeDesc& exd,
                          SolveParams prm, void* workspace, float* probs, void* avail, int avail_is64, int* status,
-                         void* out, int n_cta, unsigned long long grid_timeout_ns, cudaStream_t stream) {
+                         void* out, int n_cta, unsigned long long grid_timeout_ns, unsigned long long* trace,
+                         int cooperative, cudaStream_t stream) {
   if (!shape_ok(topo) || n_cta < 1) return cudaErrorInvalidValue;
   Exchange ex{exd.recv, exd.flags, exd.n_ranks, exd.my_rank, exd.timeout_ns};
   if (idx_is64) {
     FusedLaunch<int64_t> l{static_cast<const int64_t*>(idx), n, make_topo(topo), ex,
                            IpmParams{prm.max_iters, prm.tol}, static_cast<Workspace*>(workspace), probs,
                            Counter{avail, avail_is64}, status, static_cast<int64_t*>(out), n_cta, grid_timeout_ns,
-                           stream};
+                           trace, cooperative, stream};
     return dispatch_shape(topo.g, topo.d, l);
   }
   FusedLaunch<int32_t> l{static_cast<const int32_t*>(idx), n, make_topo(topo), ex,
                          IpmParams{prm.max_iters, prm.tol}, static_cast<Workspace*>(workspace), probs,
                          Counter{avail, avail_is64}, status, static_cast<int32_t*>(out), n_cta, grid_timeout_ns,
-                         stream};
+                         trace, cooperative, stream};
   return dispatch_shape(topo.g, topo.d, l);
 }
 

@@ -353,6 +353,21 @@ class Planner:
             self._engine.status().zero_()
         return out
 
+    def enable_trace(self, on: bool = True) -> None:
+        """Make the fused kernel write per-phase ``globaltimer`` stamps (a few extra stores)."""
+        if self._engine is not None:
+            self._engine.enable_trace(bool(on))
+
+    def phase_times_us(self) -> dict[str, float] | None:
+        """Phase durations of the last fused ``run`` in microseconds; synchronises."""
+        if self._engine is None or self._engine.trace() is None:
+            return None
+        t = self._engine.trace().cpu().tolist()
+        names = ["count", "grid_barrier", "exchange", "solve", "redirect", "drain"]
+        out = {n: (t[i + 1] - t[i]) / 1e3 for i, n in enumerate(names)}
+        out["total"] = (t[6] - t[0]) / 1e3
+        return out
+
     # ------------------------------------------------------------------ checkpointing
     def state_dict(self) -> dict[str, Any]:
         """Everything needed to resume with the same placement (the reference keeps no

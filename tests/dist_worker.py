@@ -1,0 +1,109 @@
+"""Worker run by tests/test_multigpu.py under torch.distributed.run (one rank per GPU).
+
+Checks the in-kernel NVLink statistics exchange against ``torch.distributed.all_reduce``,
+that every rank computes identical shares, and that a rank which skips a step makes the
+others' bounded wait run out, report, and recover after a collective reset.
+"""
+
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+from lplb_b200 import Planner, cube, lp  # noqa: E402
+
+
+def main():
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    local = int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    group = dist.group.WORLD
+
+    planner = Planner(cube(), 256 + 16, 256, 8, group, device=dev, comm="p2p", peer_timeout_us=2e5)
+    assert planner.comm == "p2p" and planner.deep_ep_initialized
+
+    # 1. stand-alone exchange is bitwise equal to NCCL's all-reduce, many times in a row
+    gen = torch.Generator(device=dev).manual_seed(100 + rank)
+    for step in range(20):
+        mine = torch.randint(0, 5000, (256,), device=dev, generator=gen, dtype=torch.int32)
+        want = mine.clone()
+        dist.all_reduce(want, group=group)
+        got = planner._engine.all_reduce_counts(mine)
+        assert torch.equal(got, want), f"rank {rank} step {step}: exchange differs from all_reduce"
+
+    # 2. fused run: global statistics, identical shares on every rank, balanced result
+    bias = torch.randn(256, device=dev, generator=torch.Generator(device=dev).manual_seed(7))
+    hist = None
+    for step in range(12):
+        logits = torch.randn(4096, 256, device=dev, generator=gen) + bias
+        idx = logits.bfloat16().topk(8, dim=-1).indices
+        counts = torch.bincount(idx.reshape(-1), minlength=256)
+        dist.all_reduce(counts, group=group)
+        if step == 2:
+            planner.update_redundancy_mapping(counts)  # same on every rank
+        avail = torch.zeros(1, dtype=torch.int32, device=dev)
+        out = planner.run(idx, avail, 148 if step % 2 else 37)
+        assert int(avail) == 1
+        ws = planner._engine.workspace()
+        assert torch.equal(ws[8 + 2 * 256 : 8 + 3 * 256].long(), counts), f"rank {rank}: global counts differ"
+        probs = planner.last_probs.clone()
+        gathered = [torch.empty_like(probs) for _ in range(world)]
+        dist.all_gather(gathered, probs, group=group)
+        assert all(torch.equal(g, probs) for g in gathered), "shares differ between ranks"
+        pl = planner.n_local_routed_experts
+        load = torch.bincount(out.reshape(-1) // pl, minlength=8).double()
+        dist.all_reduce(load, group=group)
+        w, fixed = lp.bundle_loads(counts.cpu().double(), planner.phy2log.cpu(), 1, 8, 2, 32, 1)
+        _, t_opt = lp.solve_highs(w[0], fixed[0], cube())
+        assert float(load.max()) <= t_opt * (1 + 1e-3) + 8 * world, (float(load.max()), t_opt)
+        assert planner.check_status().ok
+    hist = counts
+
+    # 3. a rank skips one step: the others' wait runs out, they report it and still route
+    dist.barrier(group=group)
+    torch.cuda.synchronize(dev)
+    logits = torch.randn(1024, 256, device=dev, generator=gen) + bias
+    idx = logits.topk(8, dim=-1).indices
+    avail = torch.zeros(1, dtype=torch.int32, device=dev)
+    if rank != world - 1:
+        out = planner.run(idx, avail)
+        torch.cuda.synchronize(dev)
+        st = planner.check_status(clear=True)
+        assert st["error"] == "peer_timeout" and st["detail"] == 1 << (world - 1), st
+        assert int(avail) == 1 and int(out.min()) >= 0
+    # the absence is learnt on the host; everybody resets the exchange before the next launch
+    planner.reset_exchange()
+    for step in range(4):
+        logits = torch.randn(1024, 256, device=dev, generator=gen) + bias
+        idx = logits.topk(8, dim=-1).indices
+        counts = torch.bincount(idx.reshape(-1), minlength=256)
+        dist.all_reduce(counts, group=group)
+        avail.zero_()
+        planner.run(idx, avail)
+        ws = planner._engine.workspace()
+        assert torch.equal(ws[8 + 2 * 256 : 8 + 3 * 256].long(), counts)
+        assert planner.check_status().ok
+
+    # 4. the NCCL pipeline gives the same shares as the fused kernel
+    staged = Planner(cube(), 256 + 16, 256, 8, group, device=dev, comm="nccl")
+    staged.load_state_dict(planner.state_dict())
+    avail.zero_()
+    out_f = planner.run(idx, avail)
+    local_counts, by_sm = staged.count_workload(idx, 148)
+    probs_s, _ = staged.solve_probs(local_counts, avail)
+    assert torch.equal(probs_s, planner.last_probs)
+
+    dist.barrier(group=group)
+    torch.cuda.synchronize(dev)
+    if rank == 0:
+        print("DIST_WORKER_OK", world)
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -108,10 +108,14 @@ def test_solver_sweep_against_oracle():
         w = torch.from_numpy(cnt[:, :, :2].astype(np.float64))
         fixed = torch.from_numpy(cnt[:, :, 2:].sum(-1).astype(np.float64))
         realised = lp.rank_loads(probs.cpu().double(), w, fixed, topology.cube()).max(-1).values
-        oracle = lp.solve_ipm(w, fixed, topology.cube(), tol=1e-9, max_iters=40)
+        oracle = lp.solve_ipm(w, fixed, topology.cube(), tol=1e-7, max_iters=40)
+        assert bool(oracle.converged.all())
         gap = (realised - oracle.t) / oracle.t
         worst = max(worst, float(gap.max()))
-        assert float(gap.min()) > -1e-7
+        assert float(gap.min()) > -1e-6
+        for i in range(0, n_group, 16):  # spot-check the oracle itself against HiGHS
+            _, t_opt = lp.solve_highs(w[i], fixed[i], topology.cube())
+            assert abs(float(oracle.t[i]) - t_opt) / t_opt < 1e-6
     assert worst < 1e-3
 
 
@@ -231,14 +235,16 @@ def test_fused_run_balances_real_routing():
     bias = torch.randn(256, device="cuda", generator=gen)
     logits = (torch.randn(4096, 256, device="cuda", generator=gen) + bias).bfloat16()
     idx = logits.topk(8, dim=-1).indices
-    planner.update_redundancy_mapping(torch.bincount(idx.reshape(-1), minlength=256))
+    # placement from an older batch with the same bias, so that it is good but not perfect
+    old = (torch.randn(4096, 256, device="cuda", generator=gen) + bias).bfloat16().topk(8, dim=-1).indices
+    planner.update_redundancy_mapping(torch.bincount(old.reshape(-1), minlength=256))
     avail = torch.zeros(1, dtype=torch.int64, device="cuda")
     out = planner.run(idx, avail)
     assert int(avail) == 1
     pl = planner.n_local_routed_experts
     before = torch.bincount(planner.mapping.log2phy[idx.reshape(-1), 0].long() // pl, minlength=8).double()
     after = torch.bincount(out.reshape(-1) // pl, minlength=8).double()
-    assert float(after.max() / after.mean()) < float(before.max() / before.mean())
+    assert float(after.max()) <= float(before.max()) + 2
     # the realised max load is the LP optimum up to rounding of quotas
     counts = torch.bincount(idx.reshape(-1), minlength=256)
     w, fixed = lp.bundle_loads(counts.cpu().double(), planner.phy2log.cpu(), 1, 8, 2, 32, 1)
