@@ -47,7 +47,7 @@ namespace py = pybind11;
 namespace {
 
 struct IpcBlock {
-  // One cudaMalloc'd region: int32 recv[2][n_ranks][E] followed by uint32 flags[n_ranks].
+  // One cudaMalloc'd region: uint64 recv[2][n_ranks][E], every word (epoch << 32) | count.
   void* base = nullptr;
   size_t bytes = 0;
 };
@@ -170,7 +170,7 @@ class PlannerEngine {
     LPLB_CHECK(limit > 0, "fused kernel cannot be resident on this device");
     if (n_cta > limit) n_cta = limit;
     auto out = torch::empty_like(idx);
-    lplb::ExchangeDesc ex{nullptr, nullptr, 1, 0, peer_timeout_ns_};
+    lplb::ExchangeDesc ex{nullptr, 1, 0, peer_timeout_ns_};
     if (use_exchange) {
       LPLB_CHECK(exchange_open_, "exchange buffers are not open; call open_exchange first");
       ex = exchange_desc();
@@ -191,9 +191,7 @@ class PlannerEngine {
     c10::cuda::CUDAGuard guard(device_);
     n_ranks_ = n_ranks;
     my_rank_ = my_rank;
-    recv_bytes_ = sizeof(int) * 2 * (size_t)n_ranks * e_;
-    recv_bytes_ = (recv_bytes_ + 255) / 256 * 256;
-    block_.bytes = recv_bytes_ + 256;
+    block_.bytes = lplb::exchange_buffer_bytes(n_ranks, e_);
     LPLB_CUDA(cudaMalloc(&block_.base, block_.bytes));
     LPLB_CUDA(cudaMemset(block_.base, 0, block_.bytes));
     LPLB_CUDA(cudaDeviceSynchronize());
@@ -207,7 +205,7 @@ class PlannerEngine {
     LPLB_CHECK(block_.base, "call alloc_exchange first");
     LPLB_CHECK((int)handles.size() == n_ranks_, "need one handle per rank");
     c10::cuda::CUDAGuard guard(device_);
-    std::vector<int64_t> recv(n_ranks_), flags(n_ranks_);
+    std::vector<int64_t> recv(n_ranks_);
     peers_.assign(n_ranks_, nullptr);
     for (int r = 0; r < n_ranks_; ++r) {
       void* base = block_.base;
@@ -219,11 +217,9 @@ class PlannerEngine {
         peers_[r] = base;
       }
       recv[r] = reinterpret_cast<int64_t>(base);
-      flags[r] = reinterpret_cast<int64_t>(static_cast<char*>(base) + recv_bytes_);
     }
     auto opts = torch::TensorOptions().dtype(torch::kInt64);
     recv_table_ = torch::from_blob(recv.data(), {n_ranks_}, opts).clone().to(torch::Device(torch::kCUDA, device_));
-    flag_table_ = torch::from_blob(flags.data(), {n_ranks_}, opts).clone().to(torch::Device(torch::kCUDA, device_));
     exchange_open_ = true;
   }
 
@@ -236,34 +232,32 @@ class PlannerEngine {
     c10::cuda::CUDAGuard guard(device_);
     n_ranks_ = n_ranks;
     my_rank_ = my_rank;
-    recv_bytes_ = (sizeof(int) * 2 * (size_t)n_ranks * e_ + 255) / 256 * 256;
-    block_.bytes = recv_bytes_ + 256;
+    block_.bytes = lplb::exchange_buffer_bytes(n_ranks, e_);
     LPLB_CUDA(cudaMalloc(&block_.base, block_.bytes));
     LPLB_CUDA(cudaMemset(block_.base, 0, block_.bytes));
     std::vector<int64_t> recv(n_ranks_, reinterpret_cast<int64_t>(block_.base));
-    std::vector<int64_t> flags(n_ranks_, reinterpret_cast<int64_t>(static_cast<char*>(block_.base) + recv_bytes_));
     auto opts = torch::TensorOptions().dtype(torch::kInt64);
     recv_table_ = torch::from_blob(recv.data(), {n_ranks_}, opts).clone().to(torch::Device(torch::kCUDA, device_));
-    flag_table_ = torch::from_blob(flags.data(), {n_ranks_}, opts).clone().to(torch::Device(torch::kCUDA, device_));
     peers_.clear();
     exchange_open_ = true;
   }
 
-  // Test hook: write `counts` into slot `rank` of both receive buffers and set that rank's
-  // arrival flag to `flag_value`.
-  void debug_fill_slot(int rank, const torch::Tensor& counts, int64_t flag_value) {
+  // Test hook: make it look as if `rank` had published `counts` for launch number `epoch`
+  // (the launch after `completed_launches()` has epoch completed + 1).
+  void debug_fill_slot(int rank, const torch::Tensor& counts, int64_t epoch) {
     LPLB_CHECK(block_.base && rank >= 0 && rank < n_ranks_, "no exchange block or bad rank");
     LPLB_CHECK(counts.numel() == e_, "counts must have E entries");
     c10::cuda::CUDAGuard guard(device_);
-    auto host = counts.to(torch::kCPU, torch::kInt32).contiguous();
+    auto words = (counts.to(torch::kCPU, torch::kInt64).contiguous() & 0xffffffffLL) + (epoch << 32);
     LPLB_CUDA(cudaDeviceSynchronize());
-    for (int parity = 0; parity < 2; ++parity) {
-      int* slot = static_cast<int*>(block_.base) + ((size_t)parity * n_ranks_ + rank) * e_;
-      LPLB_CUDA(cudaMemcpy(slot, host.data_ptr<int>(), sizeof(int) * e_, cudaMemcpyHostToDevice));
-    }
-    const uint32_t flag = (uint32_t)flag_value;
-    uint32_t* flags = reinterpret_cast<uint32_t*>(static_cast<char*>(block_.base) + recv_bytes_);
-    LPLB_CUDA(cudaMemcpy(flags + rank, &flag, sizeof(flag), cudaMemcpyHostToDevice));
+    auto* slot = static_cast<unsigned long long*>(block_.base) + ((size_t)(epoch & 1) * n_ranks_ + rank) * e_;
+    LPLB_CUDA(cudaMemcpy(slot, words.data_ptr<int64_t>(), sizeof(int64_t) * e_, cudaMemcpyHostToDevice));
+  }
+
+  // Launches (fused or stand-alone exchange) completed so far on this engine; synchronises.
+  int64_t completed_launches() {
+    c10::cuda::CUDAGuard guard(device_);
+    return (int64_t)(uint32_t)workspace_[0].item<int>();
   }
 
   // Collective by convention: every rank calls it between steps, with no launch in flight,
@@ -319,9 +313,8 @@ class PlannerEngine {
   }
 
   lplb::ExchangeDesc exchange_desc() const {
-    return lplb::ExchangeDesc{reinterpret_cast<int* const*>(recv_table_.data_ptr()),
-                              reinterpret_cast<uint32_t* const*>(flag_table_.data_ptr()), n_ranks_, my_rank_,
-                              peer_timeout_ns_};
+    return lplb::ExchangeDesc{reinterpret_cast<unsigned long long* const*>(recv_table_.data_ptr()), n_ranks_,
+                              my_rank_, peer_timeout_ns_};
   }
 
   void require_mapping() const {
@@ -353,9 +346,8 @@ class PlannerEngine {
   int max_cta64_ = -1, max_cta32_ = -1;
   // exchange
   IpcBlock block_;
-  size_t recv_bytes_ = 0;
   std::vector<void*> peers_;
-  torch::Tensor recv_table_, flag_table_;
+  torch::Tensor recv_table_;
   int n_ranks_ = 1, my_rank_ = 0;
   bool exchange_open_ = false;
   bool cooperative_ = true;
@@ -380,6 +372,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def("open_exchange", &PlannerEngine::open_exchange)
       .def("open_exchange_loopback", &PlannerEngine::open_exchange_loopback)
       .def("debug_fill_slot", &PlannerEngine::debug_fill_slot)
+      .def("completed_launches", &PlannerEngine::completed_launches)
       .def("reset_exchange", &PlannerEngine::reset_exchange)
       .def("close_exchange", &PlannerEngine::close_exchange)
       .def("exchange_open", &PlannerEngine::exchange_open)

@@ -27,10 +27,9 @@ struct Topo {
 };
 
 // Peer-memory exchange state.  recv[r] points at rank r's receive buffer
-// int32[2][n_ranks][E] (two epochs' worth), flags[r] at rank r's uint32[n_ranks].
+// uint64[2][n_ranks][E] (two epochs' worth); every word is (epoch << 32) | count.
 struct Exchange {
-  int* const* recv;
-  uint32_t* const* flags;
+  unsigned long long* const* recv;
   int n_ranks;
   int my_rank;
   unsigned long long timeout_ns;
@@ -261,38 +260,66 @@ __global__ void __launch_bounds__(kBlock) redirect_kernel(const IdxT* __restrict
 
 // ---------------------------------------------------------------------------------------
 // All-reduce of int32[E] counts over the ranks of one NVLink domain, called by one CTA.
-// Push model: every rank stores its vector into slot `my_rank` of every peer's receive
-// buffer (plain st over NVLink), then raises one flag per peer with a system-scope
-// release store; it then acquires one flag per peer and sums the slots in its own
-// memory.  Two receive buffers alternate by epoch parity: a rank can only be one launch
-// ahead of the slowest peer (it needs that peer's flag of the current epoch to finish),
-// so the buffer it overwrites is never still being read.  `mine` and `sum` are
-// shared-memory arrays of E ints.  Returns a bit mask of peers that never arrived.
+// Push model with the flag packed next to the data: every rank stores each count together
+// with the epoch as one aligned 8-byte word into slot `my_rank` of every peer's receive
+// buffer (plain st over NVLink).  An aligned 8-byte store is single-copy atomic, so a
+// reader that sees the epoch in the upper half also sees the count in the lower half; no
+// fence, no separate flag and no second NVLink round trip are needed.  Each thread then
+// polls the words of its own elements in this GPU's memory and sums them.
+// Two receive buffers alternate by epoch parity: a rank can only be one launch ahead of the
+// slowest peer (it needs that peer's words of the current epoch to finish), so the buffer
+// it overwrites is never still being read.  `mine` and `sum` are shared-memory arrays of E
+// ints.  Returns a bit mask of peers that never arrived; their share of the sum is replaced
+// by this rank's own counts.
+__device__ __forceinline__ unsigned long long ld_volatile_u64(const unsigned long long* p) {
+  unsigned long long v;
+  asm volatile("ld.volatile.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_volatile_u64(unsigned long long* p, unsigned long long v) {
+  asm volatile("st.volatile.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+
 __device__ __forceinline__ unsigned exchange_counts(const Exchange& ex, uint32_t epoch, int e, const int* mine,
                                                     int* sum) {
   __shared__ unsigned missing;
   const int parity = epoch & 1;
   if (threadIdx.x == 0) missing = 0;
-  for (int r = 0; r < ex.n_ranks; ++r) {
-    int* slot = ex.recv[r] + ((size_t)parity * ex.n_ranks + ex.my_rank) * e;
-    for (int i = threadIdx.x; i < e; i += kBlock) slot[i] = mine[i];
-  }
-  __threadfence_system();
   __syncthreads();
-  if (threadIdx.x < ex.n_ranks) {
-    st_release_sys(ex.flags[threadIdx.x] + ex.my_rank, epoch);
-    if (!bounded_wait_ge<true>(ex.flags[ex.my_rank] + threadIdx.x, epoch, ex.timeout_ns))
-      atomicOr(&missing, 1u << (threadIdx.x & 31));
+  const unsigned long long tag = (unsigned long long)epoch << 32;
+  for (int r = 0; r < ex.n_ranks; ++r) {
+    unsigned long long* slot = ex.recv[r] + ((size_t)parity * ex.n_ranks + ex.my_rank) * e;
+    for (int i = threadIdx.x; i < e; i += kBlock) st_volatile_u64(&slot[i], tag | (uint32_t)mine[i]);
   }
+  const unsigned long long* base = ex.recv[ex.my_rank] + (size_t)parity * ex.n_ranks * e;
+  // pass 1: wait until every word of this thread's elements carries the epoch
+  unsigned late = 0;
+  const uint64_t t0 = global_timer_ns();
+  for (int i = threadIdx.x; i < e; i += kBlock) {
+    for (int r = 0; r < ex.n_ranks; ++r) {
+      if ((late >> (r & 31)) & 1u) continue;
+      const unsigned long long* word = &base[(size_t)r * e + i];
+      uint32_t spins = 0;
+      while ((uint32_t)(ld_volatile_u64(word) >> 32) != epoch) {
+        if ((++spins & 63u) == 0) {
+          if (global_timer_ns() - t0 > ex.timeout_ns) {
+            late |= 1u << (r & 31);
+            break;
+          }
+          __nanosleep(100);
+        }
+      }
+    }
+  }
+  if (late) atomicOr(&missing, late);
   __syncthreads();
   const unsigned miss = missing;
-  const int* base = ex.recv[ex.my_rank] + (size_t)parity * ex.n_ranks * e;
+  // pass 2: sum; an absent peer contributes this rank's own counts instead of stale data
   for (int i = threadIdx.x; i < e; i += kBlock) {
     int acc = 0;
     for (int r = 0; r < ex.n_ranks; ++r) {
-      // a peer that never arrived contributes this rank's own counts instead of stale data
       const bool absent = (miss >> (r & 31)) & 1u;
-      acc += absent ? mine[i] : __ldcv(&base[(size_t)r * e + i]);
+      acc += absent ? mine[i] : (int)(uint32_t)ld_volatile_u64(&base[(size_t)r * e + i]);
     }
     sum[i] = acc;
   }

@@ -258,13 +258,14 @@ def test_exchange_loopback_sums_prefilled_peer():
     eng = planner._engine
     eng.open_exchange_loopback(2, 0)
     peer = torch.arange(64, dtype=torch.int32) * 3
-    eng.debug_fill_slot(1, peer, 0x3FFFFFFF)  # "rank 1 arrived for every epoch to come"
     mine = torch.randint(0, 100, (64,), dtype=torch.int32, device="cuda")
     for _ in range(3):  # both parities
+        eng.debug_fill_slot(1, peer, eng.completed_launches() + 1)  # "rank 1 has published for the next launch"
         got = eng.all_reduce_counts(mine)
         assert torch.equal(got.cpu(), mine.cpu() + peer)
     idx = torch.randint(0, 64, (4096, 4), device="cuda")
     avail = torch.zeros((), dtype=torch.int32, device="cuda")
+    eng.debug_fill_slot(1, peer, eng.completed_launches() + 1)
     out = eng.run_fused(idx, avail, 16, True)
     counts = torch.bincount(idx.reshape(-1), minlength=64).int()
     ws = eng.workspace()
