@@ -29,6 +29,7 @@ _NAME = "lplb_b200_native"
 SOURCES = [
     "binding.cpp",
     "planner_launch.cu",
+    "count_noalloc.cu",
 ]
 
 NVCC_FLAGS = [
