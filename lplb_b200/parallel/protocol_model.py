@@ -1,0 +1,107 @@
+"""Executable model of the in-kernel statistics exchange, for testing on a CPU.
+
+The kernel protocol (``exchange_counts`` in ``csrc/planner_kernels.cuh``): in launch number
+``n`` (the epoch) every rank stores, for each element, the word ``(n << 32) | count`` into
+slot ``[n & 1][my_rank]`` of every rank's receive buffer, then polls its own buffer until
+every word of parity ``n & 1`` carries tag ``n`` or a time budget runs out, then sums.  A
+rank whose words did not arrive in time is reported and replaced by the reader's own counts.
+
+The model keeps the same state and lets a test decide, store by store, when (or whether)
+each one is delivered: in order, late, twice, or never.  The only ordering assumed of the
+fabric is the one the hardware gives: two stores from one source to one address are
+delivered in program order.
+"""
+
+from __future__ import annotations
+
+import random
+from dataclasses import dataclass, field
+
+__all__ = ["Fabric", "Rank", "run_lockstep"]
+
+
+@dataclass
+class Store:
+    src: int
+    dst: int
+    parity: int
+    elem: int
+    word: int
+
+
+@dataclass
+class Fabric:
+    """In-flight stores, one FIFO per (src, dst, address)."""
+
+    n_ranks: int
+    n_elems: int
+    queues: dict = field(default_factory=dict)
+    dropped_sources: set = field(default_factory=set)
+
+    def send(self, st: Store) -> None:
+        if st.src in self.dropped_sources and st.dst != st.src:
+            return
+        self.queues.setdefault((st.src, st.dst, st.parity, st.elem), []).append(st)
+
+    def pending(self) -> list:
+        return [k for k, q in self.queues.items() if q]
+
+    def deliver(self, key, ranks, duplicate: bool = False) -> None:
+        st = self.queues[key][0] if duplicate else self.queues[key].pop(0)
+        ranks[st.dst].recv[st.parity][st.src][st.elem] = st.word
+
+    def deliver_all(self, ranks, rng: random.Random | None = None) -> None:
+        keys = self.pending()
+        while keys:
+            key = rng.choice(keys) if rng else keys[0]
+            self.deliver(key, ranks)
+            keys = self.pending()
+
+
+class Rank:
+    def __init__(self, rank: int, n_ranks: int, n_elems: int):
+        self.rank, self.n_ranks, self.n_elems = rank, n_ranks, n_elems
+        self.epoch = 0
+        self.recv = [[[0] * n_elems for _ in range(n_ranks)] for _ in range(2)]
+        self.mine: list[int] = [0] * n_elems
+
+    def publish(self, counts: list[int], fabric: Fabric) -> int:
+        """First half of a launch: bump the epoch and push the words."""
+        self.epoch += 1
+        self.mine = list(counts)
+        for dst in range(self.n_ranks):
+            for e, c in enumerate(counts):
+                fabric.send(Store(self.rank, dst, self.epoch & 1, e, (self.epoch << 32) | (c & 0xFFFFFFFF)))
+        return self.epoch
+
+    def ready(self) -> list[bool]:
+        """Per source rank: do all words of the current parity carry the current epoch?"""
+        buf = self.recv[self.epoch & 1]
+        return [all((w >> 32) == self.epoch for w in buf[src]) for src in range(self.n_ranks)]
+
+    def finish(self) -> tuple[list[int], int]:
+        """Second half: sum what arrived; returns ``(sums, missing bit mask)``."""
+        ok = self.ready()
+        buf = self.recv[self.epoch & 1]
+        miss = sum(1 << r for r in range(self.n_ranks) if not ok[r])
+        sums = [
+            sum((buf[src][e] & 0xFFFFFFFF) if ok[src] else self.mine[e] for src in range(self.n_ranks))
+            for e in range(self.n_elems)
+        ]
+        return sums, miss
+
+
+def run_lockstep(n_ranks: int, n_elems: int, steps: int, seed: int = 0):
+    """All ranks publish, the fabric delivers in random order, all ranks finish; repeated."""
+    rng = random.Random(seed)
+    ranks = [Rank(r, n_ranks, n_elems) for r in range(n_ranks)]
+    fabric = Fabric(n_ranks, n_elems)
+    history = []
+    for _ in range(steps):
+        counts = [[rng.randrange(0, 1 << 20) for _ in range(n_elems)] for _ in range(n_ranks)]
+        for r in ranks:
+            r.publish(counts[r.rank], fabric)
+        fabric.deliver_all(ranks, rng)
+        results = [r.finish() for r in ranks]
+        history.append((counts, results))
+    return history
