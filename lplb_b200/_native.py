@@ -30,6 +30,8 @@ SOURCES = [
     "binding.cpp",
     "planner_launch.cu",
     "count_noalloc.cu",
+    "moe_binding.cpp",
+    "moe_launch.cu",
 ]
 
 NVCC_FLAGS = [

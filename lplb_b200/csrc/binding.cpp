@@ -355,6 +355,8 @@ class PlannerEngine {
 
 }  // namespace
 
+void bind_moe(py::module_& m);  // moe_binding.cpp
+
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.doc() = "lplb_b200 native runtime (sm_100a)";
   py::class_<PlannerEngine>(m, "PlannerEngine")
@@ -384,6 +386,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def("workspace", &PlannerEngine::workspace)
       .def("n_logical", &PlannerEngine::n_logical)
       .def("max_fused_ctas", &PlannerEngine::max_fused_ctas);
+  bind_moe(m);
   m.attr("MAX_GROUP_SIZE") = lplb::kMaxGroupSize;
   m.attr("MAX_DUP") = lplb::kMaxDup;
   m.attr("MAX_LOGICAL_EXPERTS") = lplb::kMaxLogicalExperts;
