@@ -38,7 +38,9 @@ constexpr int kBM = 128, kBN = 256, kBK = 64, kStages = 4, kUmmaK = 16;
 constexpr int kGemmThreads = 192;
 constexpr int kTmemCols = 512;
 constexpr uint32_t kStageBytesA = kBM * kBK * 2, kStageBytesB = kBN * kBK * 2;
-constexpr size_t kGemmSmem = 1024 + (size_t)kStages * (kStageBytesA + kStageBytesB) + 256;
+// per epilogue warp: 32 rows x 128 bf16 columns, staged so that rows leave as 256-byte segments
+constexpr uint32_t kStageOutBytes = 32 * 128 * 2;
+constexpr size_t kGemmSmem = 1024 + (size_t)kStages * (kStageBytesA + kStageBytesB) + 256 + 4 * kStageOutBytes;
 constexpr int kMaxLocalExperts = 64;
 constexpr int kMaxRanks = 8;
 
@@ -109,6 +111,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   uint8_t* smem_a = smem;
   uint8_t* smem_b = smem + kStages * kStageBytesA;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem_b + kStages * kStageBytesB);
+  uint8_t* smem_out = smem_b + kStages * kStageBytesB + 256;  // 4 x kStageOutBytes, 256-byte aligned
   // bars: full[kStages], empty[kStages], tmem_full[2], tmem_empty[2]
   const uint32_t bar_full = smem_u32(bars), bar_empty = smem_u32(bars + kStages);
   const uint32_t bar_tfull = smem_u32(bars + 2 * kStages), bar_tempty = smem_u32(bars + 2 * kStages + 2);
@@ -252,25 +255,45 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           }
         }
       } else {
-        __nv_bfloat16* dst = nullptr;
+        // Each lane owns one output row in TMEM, but a row's 512 bytes should leave the SM
+        // as long contiguous stores (they cross NVLink).  Stage 32 rows x 128 columns in
+        // shared memory (16-byte chunks XOR-swizzled by row against bank conflicts), then
+        // let 16 lanes write one row's 256 bytes: two rows per store instruction.
+        unsigned long long dst_addr = 0;
         if (valid) {
           const int mt = args.meta[row];
-          dst = args.comb[(mt >> 20) & (kMaxRanks - 1)] + (size_t)(mt & 0xFFFFF) * args.out_ld + (size_t)n * kBN;
+          dst_addr = reinterpret_cast<unsigned long long>(args.comb[(mt >> 20) & (kMaxRanks - 1)] +
+                                                          (size_t)(mt & 0xFFFFF) * args.out_ld + (size_t)n * kBN);
         }
+        uint8_t* stage = smem_out + (warp - 2) * kStageOutBytes;
 #pragma unroll 1
-        for (int c0 = 0; c0 < kBN; c0 += 32) {
-          uint32_t v[32];
-          tmem_ld32(taddr + c0, v);
-          tmem_ld_wait();
-          if (valid) {
+        for (int half = 0; half < 2; ++half) {
+#pragma unroll 1
+          for (int c0 = 0; c0 < 128; c0 += 32) {
+            uint32_t v[32];
+            tmem_ld32(taddr + half * 128 + c0, v);
+            tmem_ld_wait();
 #pragma unroll
             for (int j = 0; j < 32; j += 8) {
-              st_global_v4(dst + c0 + j, pack_bf16(__uint_as_float(v[j]), __uint_as_float(v[j + 1])),
-                           pack_bf16(__uint_as_float(v[j + 2]), __uint_as_float(v[j + 3])),
-                           pack_bf16(__uint_as_float(v[j + 4]), __uint_as_float(v[j + 5])),
-                           pack_bf16(__uint_as_float(v[j + 6]), __uint_as_float(v[j + 7])));
+              const int chunk = (c0 + j) >> 3;  // 16-byte chunk index within the 256-byte row
+              uint4 o;
+              o.x = pack_bf16(__uint_as_float(v[j]), __uint_as_float(v[j + 1]));
+              o.y = pack_bf16(__uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
+              o.z = pack_bf16(__uint_as_float(v[j + 4]), __uint_as_float(v[j + 5]));
+              o.w = pack_bf16(__uint_as_float(v[j + 6]), __uint_as_float(v[j + 7]));
+              *reinterpret_cast<uint4*>(stage + lane * 256 + ((chunk ^ (lane & 15)) << 4)) = o;
             }
           }
+          __syncwarp();
+#pragma unroll 4
+          for (int i = 0; i < 16; ++i) {
+            const int r = 2 * i + (lane >> 4), chunk = lane & 15;
+            const unsigned long long base = __shfl_sync(0xffffffffu, dst_addr, r);
+            const uint4 o = *reinterpret_cast<const uint4*>(stage + r * 256 + ((chunk ^ (r & 15)) << 4));
+            if (base != 0)
+              st_global_v4(reinterpret_cast<void*>(base + (size_t)half * 256 + (size_t)chunk * 16), o.x, o.y, o.z, o.w);
+          }
+          __syncwarp();
         }
       }
       tc_fence_before_sync();

@@ -98,6 +98,37 @@ def main():
     probs_s, _ = staged.solve_probs(local_counts, avail)
     assert torch.equal(probs_s, planner.last_probs)
 
+    # 5. expert-parallel MoE layer over the same ranks: dispatch and combine cross NVLink
+    from lplb_b200 import ring
+    from lplb_b200.models.moe import MoELayer
+
+    r2o = cube() if world == 8 else ring(world)
+    red = r2o.shape[1]
+    n_logical = 4 * world
+    mp = Planner(r2o, n_logical + red * world, n_logical, world, group, device=dev, comm="p2p")
+    layer = MoELayer(mp, 512, 256, 4, max_tokens=512, group=group, capacity_factor=4.0)
+    layer.engine.set_timeout_us(2e5)
+    single = Planner(r2o, n_logical + red * world, n_logical, world, device=dev)  # reference weights only
+    ref_layer = MoELayer(single, 512, 256, 4, max_tokens=512)
+    for step in range(4):
+        g2 = torch.Generator(device=dev).manual_seed(1000 * step + rank)
+        tokens = 300 + 17 * rank
+        x = torch.randn(tokens, 512, device=dev, generator=g2).bfloat16()
+        logits = torch.randn(tokens, n_logical, device=dev, generator=g2) + torch.linspace(-1, 1, n_logical, device=dev)
+        w, idx = torch.softmax(logits, -1).topk(4, dim=-1)
+        if step == 1:
+            hist = torch.bincount(idx.reshape(-1), minlength=n_logical)
+            dist.all_reduce(hist, group=group)
+            mp.update_redundancy_mapping(hist)
+            layer.place_weights()
+        avail.zero_()
+        out = layer.forward(x, idx, w, avail, "lplb" if step % 2 == 0 else "static")
+        torch.cuda.synchronize(dev)
+        assert layer.check() == 0, layer.engine.status().tolist()
+        ref = ref_layer.reference_forward(x, idx, w).float()
+        err = float((out.float() - ref).abs().max() / ref.abs().max())
+        assert err < 2e-2, f"rank {rank} step {step}: MoE output differs from the reference by {err}"
+
     dist.barrier(group=group)
     torch.cuda.synchronize(dev)
     if rank == 0:
