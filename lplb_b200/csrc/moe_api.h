@@ -36,6 +36,7 @@ struct LayerBuffers {
   void* act;                           // bf16 [capacity, I]
   int* plan;                           // int32 plan block, see plan_words()
   int* by_cta;                         // int32 [n_cta, n_ranks * n_local] prefix rows of the pair histogram
+  int* pair_slot;                      // int32 [max_tokens * topk] return slot of every pair
   void* planner_workspace;             // counting kernel workspace (ticket)
   unsigned* tickets;                   // uint32 [4], zero
   int* status;                         // int32 [16]
@@ -64,10 +65,9 @@ cudaError_t launch_dispatch(const LayerShape& sh, const LayerBuffers& b, const v
 cudaError_t launch_gemm(const LayerShape& sh, const LayerBuffers& b, const CUtensorMap& tmap_a,
                         const CUtensorMap& tmap_b, int which, uint32_t epoch, unsigned long long timeout_ns,
                         int n_cta, cudaStream_t stream);
-// Step 5: out[t] = sum_k weight[t, k] * comb[t * topk + k].
-cudaError_t launch_combine(const LayerShape& sh, const LayerBuffers& b, const float* weights, const void* phys_idx,
-                           int idx_is64, void* out, int n_tokens, uint32_t epoch, unsigned long long timeout_ns,
-                           int n_cta, cudaStream_t stream);
+// Step 5: out[t] = sum_k weight[t, k] * comb[pair_slot[t * topk + k]].
+cudaError_t launch_combine(const LayerShape& sh, const LayerBuffers& b, const float* weights, void* out, int n_tokens,
+                           uint32_t epoch, unsigned long long timeout_ns, int n_cta, cudaStream_t stream);
 
 }  // namespace moe
 }  // namespace lplb

@@ -89,6 +89,7 @@ class MoeEngine {
     plan_ = torch::zeros({lplb::moe::plan_words(sh_.n_ranks, sh_.n_local)}, i32);
     workspace_ = torch::zeros({(int64_t)((lplb::planner_workspace_bytes(p_) + 3) / 4)}, i32);
     tickets_ = torch::zeros({4}, i32);
+    pair_slot_ = torch::full({(int64_t)sh_.max_tokens * sh_.topk}, -1, i32);
     status_ = torch::zeros({16}, i32);
     MOE_CUDA(cudaDeviceSynchronize());
     cudaIpcMemHandle_t handle;
@@ -191,8 +192,8 @@ class MoeEngine {
     if (upto <= 3) return out;
     MOE_CUDA(lplb::moe::launch_gemm(sh_, buf_, tm_act_, tm_w2_, 1, epoch_, timeout_ns_, gemm_ctas(), s));
     if (upto <= 4) return out;
-    MOE_CUDA(lplb::moe::launch_combine(sh_, buf_, weights.data_ptr<float>(), phys_idx.data_ptr(), is64,
-                                       out.data_ptr(), n_tokens, epoch_, timeout_ns_, 4 * sm_count(), s));
+    MOE_CUDA(lplb::moe::launch_combine(sh_, buf_, weights.data_ptr<float>(), out.data_ptr(), n_tokens, epoch_,
+                                       timeout_ns_, 4 * sm_count(), s));
     return out;
   }
 
@@ -200,6 +201,7 @@ class MoeEngine {
   torch::Tensor status() const { return status_; }
   torch::Tensor plan() const { return plan_; }
   torch::Tensor act() const { return act_; }
+  torch::Tensor pair_slot() const { return pair_slot_; }
   int64_t epoch() const { return epoch_; }
 
   // Views of this rank's peer-visible buffers (for tests).
@@ -235,6 +237,7 @@ class MoeEngine {
     buf_.act = act_.data_ptr();
     buf_.plan = plan_.data_ptr<int>();
     buf_.by_cta = nullptr;
+    buf_.pair_slot = pair_slot_.data_ptr<int>();
     buf_.planner_workspace = workspace_.data_ptr();
     buf_.tickets = reinterpret_cast<unsigned*>(tickets_.data_ptr<int>());
     buf_.status = status_.data_ptr<int>();
@@ -248,7 +251,7 @@ class MoeEngine {
   void* block_ = nullptr;
   std::vector<char*> bases_;
   std::vector<void*> opened_;
-  torch::Tensor act_, plan_, workspace_, tickets_, status_, by_cta_, w13_, w2_;
+  torch::Tensor act_, plan_, workspace_, tickets_, status_, by_cta_, pair_slot_, w13_, w2_;
   CUtensorMap tm_x_{}, tm_w13_{}, tm_act_{}, tm_w2_{};
   bool ready_ = false, have_weights_ = false;
   uint32_t epoch_ = 0;
@@ -273,6 +276,7 @@ void bind_moe(py::module_& m) {
       .def("status", &MoeEngine::status)
       .def("plan", &MoeEngine::plan)
       .def("act", &MoeEngine::act)
+      .def("pair_slot", &MoeEngine::pair_slot)
       .def("epoch", &MoeEngine::epoch)
       .def("recv_x", &MoeEngine::recv_x)
       .def("recv_meta", &MoeEngine::recv_meta)

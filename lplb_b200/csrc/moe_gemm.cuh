@@ -20,7 +20,7 @@
 //             (the weight rows are stored in that order); writes silu(gate)*up as bf16
 //             into act[row, n_tile*128 + c].
 //   kScatter  converts to bf16 and stores each row to the buffer of the GPU the token came
-//             from (peer memory over NVLink), at slot meta[row] & 0xFFFFF: this is the
+//             from (peer memory over NVLink), at the return slot meta[row] & 0xFFFFF: this is the
 //             combine step of the MoE layer fused into the last GEMM.
 //
 // The reference has no MoE layer; this kernel exists for the end-to-end benchmark.
@@ -59,7 +59,7 @@ struct GemmArgs {
   __nv_bfloat16* act;     // [capacity, act_ld]
   int act_ld;             // N / 2
   // kScatter
-  const int* meta;        // [capacity] (src_rank << 20) | (token * topk + k)
+  const int* meta;        // [capacity] (src_rank << 20) | return slot on the source rank
   __nv_bfloat16* comb[kMaxRanks];  // per source rank: [tokens * topk, out_ld]
   int out_ld;             // N
   // cross-GPU flags (epoch valued).  wait_flags: this rank's array [n_ranks], all must reach

@@ -84,6 +84,7 @@ cudaError_t launch_dispatch(const LayerShape& sh, const LayerBuffers& b, const v
   a.idx = phys_idx;
   a.dst_row_start = b.plan + 2 * sh.n_local;
   a.by_cta = b.by_cta;
+  a.pair_slot = b.pair_slot;
   a.ticket = b.tickets + 0;
   a.n_pairs = (long long)n_tokens * sh.topk;
   a.idx_is64 = idx_is64;
@@ -94,7 +95,7 @@ cudaError_t launch_dispatch(const LayerShape& sh, const LayerBuffers& b, const v
   a.my_rank = sh.my_rank;
   a.capacity = sh.capacity;
   a.epoch = epoch;
-  const size_t smem = sizeof(int) * (2 * (size_t)P + kDispatchChunk);
+  const size_t smem = sizeof(int) * (3 * (size_t)P + kDispatchChunk);
   dispatch_kernel<<<n_cta, kSupportThreads, smem, stream>>>(a);
   return cudaGetLastError();
 }
@@ -145,18 +146,16 @@ cudaError_t launch_gemm(const LayerShape& sh, const LayerBuffers& b, const CUten
   return cudaGetLastError();
 }
 
-cudaError_t launch_combine(const LayerShape& sh, const LayerBuffers& b, const float* weights, const void* phys_idx,
-                           int idx_is64, void* out, int n_tokens, uint32_t epoch, unsigned long long timeout_ns,
-                           int n_cta, cudaStream_t stream) {
+cudaError_t launch_combine(const LayerShape& sh, const LayerBuffers& b, const float* weights, void* out, int n_tokens,
+                           uint32_t epoch, unsigned long long timeout_ns, int n_cta, cudaStream_t stream) {
   if (!shape_ok(sh) || n_tokens < 0 || n_tokens > sh.max_tokens || n_cta < 1) return cudaErrorInvalidValue;
   CombineArgs a{};
   a.comb = static_cast<const __nv_bfloat16*>(b.comb[sh.my_rank]);
   a.weights = weights;
-  a.idx = phys_idx;
+  a.pair_slot = b.pair_slot;
   a.out = static_cast<__nv_bfloat16*>(out);
   a.wait_flags = b.flags[sh.my_rank] + sh.n_ranks;
   a.status = b.status;
-  a.idx_is64 = idx_is64;
   a.n_tokens = n_tokens;
   a.topk = sh.topk;
   a.hidden = sh.hidden;

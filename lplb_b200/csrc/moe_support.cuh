@@ -118,6 +118,7 @@ struct DispatchArgs {
   const void* idx;                   // [tokens * topk] physical expert ids, -1 = skip
   const int* dst_row_start;          // [P]
   const int* by_cta;                 // [n_cta, P] inclusive prefix rows from the counting kernel
+  int* pair_slot;                    // [tokens * topk] out: return slot of every pair, -1 = dropped
   unsigned* ticket;
   long long n_pairs;
   int idx_is64, topk, hidden, n_local, n_ranks, my_rank, capacity;
@@ -130,16 +131,38 @@ constexpr int kDispatchChunk = 1024;
 // kernel, so by_cta[p-1] is where its ordinals start.  Rows go straight into the target
 // rank's receive buffer with 16-byte stores over NVLink; the last CTA to finish raises this
 // rank's "dispatch done" flag on every peer.
+//
+// Return path: the k-th pair this rank sends to physical expert e gets return slot
+// send_base[e] + k, where send_base is the exclusive prefix of this rank's own counts.  The
+// slot travels with the row (meta), and the expert's rank writes the result row to that slot
+// of this rank's return buffer.  Consecutive rows of an expert therefore come back to
+// consecutive slots: the stores that cross NVLink walk through memory sequentially, the same
+// way the dispatch stores do, instead of hitting a random page per row.
 __global__ void __launch_bounds__(kSupportThreads) dispatch_kernel(const DispatchArgs a) {
   extern __shared__ int sm[];
   const int P = a.n_ranks * a.n_local;
   int* cur = sm;            // [P] next ordinal per physical expert
   int* dst_start = sm + P;  // [P]
   int* target = sm + 2 * P; // [kDispatchChunk] (rank << 24) | row, or -1
+  int* send_base = target + kDispatchChunk;  // [P]
   const int p = blockIdx.x, n_cta = gridDim.x;
   for (int i = threadIdx.x; i < P; i += kSupportThreads) {
     cur[i] = p == 0 ? 0 : a.by_cta[(size_t)(p - 1) * P + i];
     dst_start[i] = a.dst_row_start[i];
+  }
+  if (threadIdx.x < 32) {  // exclusive prefix of this rank's totals, one warp
+    int carry = 0;
+    for (int i0 = 0; i0 < P; i0 += 32) {
+      const int i = i0 + threadIdx.x;
+      const int v = i < P ? a.by_cta[(size_t)(n_cta - 1) * P + i] : 0;
+      int inc = v;
+      for (int o = 1; o < 32; o <<= 1) {
+        const int up = __shfl_up_sync(0xffffffffu, inc, o);
+        if ((int)threadIdx.x >= o) inc += up;
+      }
+      if (i < P) send_base[i] = carry + inc - v;
+      carry += __shfl_sync(0xffffffffu, inc, 31);
+    }
   }
   __syncthreads();
   const long long begin = slice_begin(a.n_pairs, p, n_cta, kSupportThreads);
@@ -151,15 +174,18 @@ __global__ void __launch_bounds__(kSupportThreads) dispatch_kernel(const Dispatc
     for (int j = threadIdx.x; j < n; j += kSupportThreads) {
       const long long i = c0 + j;
       const long long e = a.idx_is64 ? ((const long long*)a.idx)[i] : (long long)((const int*)a.idx)[i];
-      int t = -1;
+      int t = -1, slot = -1;
       if (e >= 0 && e < P) {
-        const int row = dst_start[e] + atomicAdd(&cur[e], 1);
+        const int k = atomicAdd(&cur[e], 1);
+        const int row = dst_start[e] + k;
         if (row < a.capacity) {
           const int dr = (int)e / a.n_local;
           t = (dr << 24) | row;
-          a.recv_meta[dr][row] = (a.my_rank << 20) | (int)i;
+          slot = send_base[e] + k;
+          a.recv_meta[dr][row] = (a.my_rank << 20) | slot;
         }
       }
+      a.pair_slot[i] = slot;
       target[j] = t;
     }
     __syncthreads();
@@ -187,16 +213,16 @@ __global__ void __launch_bounds__(kSupportThreads) dispatch_kernel(const Dispatc
 struct CombineArgs {
   const __nv_bfloat16* comb;  // [tokens * topk, hidden] rows written by the experts' ranks
   const float* weights;       // [tokens, topk]
-  const void* idx;            // [tokens * topk]; pairs with id -1 contribute nothing
+  const int* pair_slot;       // [tokens * topk] row of `comb` that holds each pair's result, -1 = none
   __nv_bfloat16* out;         // [tokens, hidden]
   const uint32_t* wait_flags; // this rank's "combine done" flags [n_ranks]
   int* status;
-  int idx_is64, n_tokens, topk, hidden, n_ranks;
+  int n_tokens, topk, hidden, n_ranks;
   uint32_t epoch;
   unsigned long long timeout_ns;
 };
 
-// out[t] = sum_k weights[t, k] * comb[t * topk + k], fp32 accumulation, after every rank has
+// out[t] = sum_k weights[t, k] * comb[pair_slot[t * topk + k]], fp32 accumulation, after every rank has
 // signalled that its expert outputs for this launch are in place.
 __global__ void __launch_bounds__(kSupportThreads) combine_kernel(const CombineArgs a) {
   __shared__ int ok;
@@ -222,10 +248,10 @@ __global__ void __launch_bounds__(kSupportThreads) combine_kernel(const CombineA
       float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
       for (int k = 0; k < a.topk; ++k) {
         const long long pair = (long long)t * a.topk + k;
-        const long long e = a.idx_is64 ? ((const long long*)a.idx)[pair] : (long long)((const int*)a.idx)[pair];
-        if (e < 0) continue;
+        const int slot = a.pair_slot[pair];
+        if (slot < 0) continue;
         const float w = a.weights[pair];
-        const uint4 raw = __ldcg(reinterpret_cast<const uint4*>(a.comb + (size_t)pair * a.hidden) + v);
+        const uint4 raw = __ldcg(reinterpret_cast<const uint4*>(a.comb + (size_t)slot * a.hidden) + v);
         const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
 #pragma unroll
         for (int q = 0; q < 4; ++q) {

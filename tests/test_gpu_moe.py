@@ -52,8 +52,17 @@ def test_dispatch_places_every_pair_in_its_experts_rows():
     total = int(rows.sum())
     meta = layer.engine.recv_meta()[:total].long()
     assert int((meta >> 20).max()) == 0  # source rank 0
-    pair = meta & 0xFFFFF
-    assert sorted(pair.tolist()) == valid.reshape(-1).nonzero().reshape(-1).tolist()  # each pair exactly once
+    slot = meta & 0xFFFFF  # return slot of every received row
+    assert sorted(slot.tolist()) == list(range(total))  # a permutation of the return slots
+    pair_slot = layer.engine.pair_slot()[: phys.numel()].long()
+    assert torch.equal(pair_slot >= 0, valid.reshape(-1))
+    pair_of_slot = torch.empty(total, dtype=torch.long, device="cuda")
+    pair_of_slot[pair_slot[pair_slot >= 0]] = (pair_slot >= 0).nonzero().reshape(-1)
+    pair = pair_of_slot[slot]  # the (token, k) pair behind every received row
+    # rows of one expert return to consecutive slots
+    for s0, n in zip(start.tolist(), rows.tolist()):
+        if n:
+            assert slot[s0 : s0 + n].tolist() == list(range(int(slot[s0]), int(slot[s0]) + n))
     assert torch.equal(layer.engine.recv_x()[:total], x[pair // 4])
     owner = torch.repeat_interleave(torch.arange(nl), rows).cuda()
     assert torch.equal(phys.reshape(-1)[pair], owner)
