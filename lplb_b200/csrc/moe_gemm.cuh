@@ -41,7 +41,7 @@ constexpr uint32_t kStageBytesA = kBM * kBK * 2, kStageBytesB = kBN * kBK * 2;
 // per epilogue warp: 32 rows x 128 bf16 columns, staged so that rows leave as 256-byte segments
 constexpr uint32_t kStageOutBytes = 32 * 128 * 2;
 constexpr size_t kGemmSmem = 1024 + (size_t)kStages * (kStageBytesA + kStageBytesB) + 256 + 4 * kStageOutBytes;
-constexpr int kMaxLocalExperts = 64;
+constexpr int kMaxLocalExperts = 128;
 constexpr int kMaxRanks = 8;
 
 enum Epilogue : int { kSwiGLU = 0, kScatter = 1 };
