@@ -43,6 +43,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--skew", type=float, default=1.0)
     ap.add_argument("--capacity-factor", type=float, default=3.0)
+    ap.add_argument("--fuse-dispatch", action="store_true", help="send rows from inside the first GEMM kernel")
     ap.add_argument("--json", default="")
     args = ap.parse_args()
 
@@ -60,6 +61,7 @@ def main():
     planner = Planner(r2o, n_logical + red * world, n_logical, world, group, device=dev, comm="p2p")
     layer = MoELayer(planner, args.hidden, args.inter, args.topk, args.tokens, group=group,
                      capacity_factor=args.capacity_factor)
+    layer.fuse_dispatch = args.fuse_dispatch
     pl = planner.n_local_routed_experts
 
     total = args.warmup + args.steps
@@ -125,6 +127,7 @@ def main():
         dispatch_ms = stages[1] - stages[0]
         out = {
             "n_gpus": world,
+            "fuse_dispatch": args.fuse_dispatch,
             "topology": "cube" if world == 8 else f"ring{world}",
             "shape": {"hidden": args.hidden, "inter": args.inter, "experts": n_logical + red * world,
                       "topk": args.topk, "tokens_per_rank": args.tokens, "skew": args.skew},
@@ -132,8 +135,9 @@ def main():
             "rank_load_max_over_mean": {k: round(v[1], 4) for k, v in results.items()},
             "lplb_stage_ms": {
                 "route_count_plan": round(stages[0], 4),
-                "dispatch": round(dispatch_ms, 4),
-                "gemm1_swiglu": round(stages[2] - stages[1], 4),
+                "dispatch_alone": round(dispatch_ms, 4),
+                ("dispatch_and_gemm1_fused" if args.fuse_dispatch else "gemm1_swiglu"): round(
+                    stages[2] - (stages[0] if args.fuse_dispatch else stages[1]), 4),
                 "gemm2_combine": round(stages[3] - stages[2], 4),
                 "reduce": round(lp_ms - stages[3], 4),
             },

@@ -34,6 +34,7 @@ def main():
     ap.add_argument("--topk", type=int, default=8)
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--skew", type=float, default=0.0, help="std of the per-expert logit bias")
+    ap.add_argument("--fuse-dispatch", action="store_true")
     ap.add_argument("--json", default="")
     args = ap.parse_args()
     dev = torch.device("cuda", 0)
@@ -62,7 +63,7 @@ def main():
             flush.fill_(it & 255)
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             a.record()
-            eng.forward(x, idx, wts, n_cta, upto)
+            eng.forward(x, idx, wts, n_cta, upto, args.fuse_dispatch)
             b.record()
             torch.cuda.synchronize()
             if it >= 2:
@@ -79,6 +80,8 @@ def main():
         "reduce_ms": cum[4] - cum[3],
         "total_ms": cum[4],
     }
+    if args.fuse_dispatch:  # stage 2 ran the stand-alone dispatch; stage 3 ran dispatch and GEMM 1 in one kernel
+        stage["dispatch_and_gemm1_fused_ms"] = cum[2] - cum[0]
     rows = t * k
     f1, f2 = 2.0 * rows * h * 2 * i, 2.0 * rows * i * h
     peaks = {}

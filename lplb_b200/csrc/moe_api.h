@@ -37,16 +37,24 @@ struct LayerBuffers {
   int* plan;                           // int32 plan block, see plan_words()
   int* by_cta;                         // int32 [n_cta, n_ranks * n_local] prefix rows of the pair histogram
   int* pair_slot;                      // int32 [max_tokens * topk] return slot of every pair
+  int* send_pair;                      // int32 [max_tokens * topk] pair index at every send position
+  int* send_target;                    // int32 [max_tokens * topk] (rank << 24) | row, or -1
+  uint32_t* arrived[kApiMaxRanks];     // per rank: uint32 [n_local] rows that have landed, cumulative
   void* planner_workspace;             // counting kernel workspace (ticket)
   unsigned* tickets;                   // uint32 [4], zero
   int* status;                         // int32 [16]
 };
 
-// Layout of the plan block (ints): rows[n_local], row_start[n_local], dst_row_start[P],
-// all_counts[n_ranks * P], then {total_rows, overflow} ; P = n_ranks * n_local.
+// Layout of the plan block (ints), P = n_ranks * n_local:
+//   rows[n_local], row_start[n_local], dst_row_start[P], all_counts[n_ranks * P],
+//   tail[8] = {total_rows, overflow, n_send, ...},
+//   order_base[P]      first send position of this rank's pairs for physical expert p,
+//   send_base[P]       first return slot of this rank's pairs for physical expert p,
+//   arrive_target[n_local], arrive_cum[n_local]   cumulative rows expected per local expert
+//                      (arrive_cum persists across launches, it is never zeroed by a launch).
 inline int plan_words(int n_ranks, int n_local) {
   const int p = n_ranks * n_local;
-  return 2 * n_local + p + n_ranks * p + 8;
+  return 2 * n_local + p + n_ranks * p + 8 + 2 * p + 2 * n_local;
 }
 
 size_t gemm_smem_bytes();
@@ -57,10 +65,18 @@ int make_tensor_map(CUtensorMap* out, const void* base, uint64_t rows, uint64_t 
 
 // Step 1: all-gather the per-expert pair counts of this launch and derive row offsets.
 cudaError_t launch_plan(const LayerShape& sh, const LayerBuffers& b, int n_cta, uint32_t epoch,
-                        unsigned long long timeout_ns, cudaStream_t stream);
+                        unsigned long long timeout_ns, int fused, cudaStream_t stream);
 // Step 2: copy every (token, k) pair's hidden state into its expert's rows on the target rank.
 cudaError_t launch_dispatch(const LayerShape& sh, const LayerBuffers& b, const void* x, const void* phys_idx,
                             int idx_is64, int n_tokens, int n_cta, uint32_t epoch, cudaStream_t stream);
+// Step 2a (fused path only): decide the send order and every pair's target row and return slot.
+cudaError_t launch_schedule(const LayerShape& sh, const LayerBuffers& b, const void* phys_idx, int idx_is64,
+                            int n_tokens, int n_cta, cudaStream_t stream);
+// Step 2b+3 fused: the first grouped GEMM with four extra warps per CTA that stream this rank's
+// rows to their targets while the tensor cores work on the experts whose rows have landed.
+cudaError_t launch_dispatch_gemm(const LayerShape& sh, const LayerBuffers& b, const CUtensorMap& tmap_a,
+                                 const CUtensorMap& tmap_b, const void* x, uint32_t epoch,
+                                 unsigned long long timeout_ns, int n_cta, cudaStream_t stream);
 // Step 3/4: grouped GEMMs.  which = 0: recv_x x w13 -> SwiGLU -> act.  which = 1: act x w2 -> peers' comb.
 cudaError_t launch_gemm(const LayerShape& sh, const LayerBuffers& b, const CUtensorMap& tmap_a,
                         const CUtensorMap& tmap_b, int which, uint32_t epoch, unsigned long long timeout_ns,

@@ -66,7 +66,8 @@ class MoeEngine {
     off_comb_ = align_up(off_meta_ + (size_t)capacity * 4, 256);
     off_cnt_ = align_up(off_comb_ + (size_t)max_tokens * topk * hidden * 2, 256);
     off_flags_ = align_up(off_cnt_ + sizeof(unsigned long long) * 2 * (size_t)n_ranks * p_, 256);
-    block_bytes_ = align_up(off_flags_ + sizeof(uint32_t) * 2 * n_ranks, 256);
+    off_arrived_ = align_up(off_flags_ + sizeof(uint32_t) * 2 * n_ranks, 256);
+    block_bytes_ = align_up(off_arrived_ + sizeof(uint32_t) * n_local, 256);
   }
 
   ~MoeEngine() {
@@ -90,6 +91,8 @@ class MoeEngine {
     workspace_ = torch::zeros({(int64_t)((lplb::planner_workspace_bytes(p_) + 3) / 4)}, i32);
     tickets_ = torch::zeros({4}, i32);
     pair_slot_ = torch::full({(int64_t)sh_.max_tokens * sh_.topk}, -1, i32);
+    send_pair_ = torch::zeros({(int64_t)sh_.max_tokens * sh_.topk}, i32);
+    send_target_ = torch::full({(int64_t)sh_.max_tokens * sh_.topk}, -1, i32);
     status_ = torch::zeros({16}, i32);
     MOE_CUDA(cudaDeviceSynchronize());
     cudaIpcMemHandle_t handle;
@@ -161,7 +164,7 @@ class MoeEngine {
   // ids (-1 = dropped), weights: [T, topk] float32.  `upto` stops after a stage for tests:
   // 1 plan, 2 dispatch, 3 first GEMM, 4 second GEMM, 5 (default) everything.
   torch::Tensor forward(const torch::Tensor& x, const torch::Tensor& phys_idx, const torch::Tensor& weights,
-                        int n_cta, int upto) {
+                        int n_cta, int upto, bool fuse_dispatch) {
     MOE_CHECK(ready_ && have_weights_, "engine is not ready: open peers and set weights first");
     MOE_CHECK(x.is_cuda() && x.scalar_type() == torch::kBFloat16 && x.is_contiguous() && x.dim() == 2 &&
                   x.size(1) == sh_.hidden && x.size(0) <= sh_.max_tokens,
@@ -184,11 +187,20 @@ class MoeEngine {
     auto out = torch::empty({n_tokens, sh_.hidden}, x.options());
     MOE_CUDA(lplb::launch_count(phys_idx.data_ptr(), is64, phys_idx.numel(), p_, n_cta, buf_.by_cta,
                                 workspace_.data_ptr(), status_.data_ptr<int>() + 8, s));
-    MOE_CUDA(lplb::moe::launch_plan(sh_, buf_, n_cta, epoch_, timeout_ns_, s));
+    // The fused path cannot stop between dispatch and the first GEMM: stage 2 then means both.
+    const bool fused = fuse_dispatch && upto >= 3;
+    MOE_CUDA(lplb::moe::launch_plan(sh_, buf_, n_cta, epoch_, timeout_ns_, fused ? 1 : 0, s));
     if (upto <= 1) return out;
-    MOE_CUDA(lplb::moe::launch_dispatch(sh_, buf_, x.data_ptr(), phys_idx.data_ptr(), is64, n_tokens, n_cta, epoch_, s));
-    if (upto <= 2) return out;
-    MOE_CUDA(lplb::moe::launch_gemm(sh_, buf_, tm_x_, tm_w13_, 0, epoch_, timeout_ns_, gemm_ctas(), s));
+    if (fused) {
+      MOE_CUDA(lplb::moe::launch_schedule(sh_, buf_, phys_idx.data_ptr(), is64, n_tokens, n_cta, s));
+      MOE_CUDA(lplb::moe::launch_dispatch_gemm(sh_, buf_, tm_x_, tm_w13_, x.data_ptr(), epoch_, timeout_ns_,
+                                               gemm_ctas(), s));
+    } else {
+      MOE_CUDA(lplb::moe::launch_dispatch(sh_, buf_, x.data_ptr(), phys_idx.data_ptr(), is64, n_tokens, n_cta,
+                                          epoch_, s));
+      if (upto <= 2) return out;
+      MOE_CUDA(lplb::moe::launch_gemm(sh_, buf_, tm_x_, tm_w13_, 0, epoch_, timeout_ns_, gemm_ctas(), s));
+    }
     if (upto <= 3) return out;
     MOE_CUDA(lplb::moe::launch_gemm(sh_, buf_, tm_act_, tm_w2_, 1, epoch_, timeout_ns_, gemm_ctas(), s));
     if (upto <= 4) return out;
@@ -233,11 +245,14 @@ class MoeEngine {
       buf_.comb[r] = base + off_comb_;
       buf_.cnt_words[r] = reinterpret_cast<unsigned long long*>(base + off_cnt_);
       buf_.flags[r] = reinterpret_cast<uint32_t*>(base + off_flags_);
+      buf_.arrived[r] = reinterpret_cast<uint32_t*>(base + off_arrived_);
     }
     buf_.act = act_.data_ptr();
     buf_.plan = plan_.data_ptr<int>();
     buf_.by_cta = nullptr;
     buf_.pair_slot = pair_slot_.data_ptr<int>();
+    buf_.send_pair = send_pair_.data_ptr<int>();
+    buf_.send_target = send_target_.data_ptr<int>();
     buf_.planner_workspace = workspace_.data_ptr();
     buf_.tickets = reinterpret_cast<unsigned*>(tickets_.data_ptr<int>());
     buf_.status = status_.data_ptr<int>();
@@ -247,11 +262,11 @@ class MoeEngine {
   lplb::moe::LayerShape sh_{};
   lplb::moe::LayerBuffers buf_{};
   int device_, p_ = 0, sms_ = 0;
-  size_t off_recv_x_ = 0, off_meta_ = 0, off_comb_ = 0, off_cnt_ = 0, off_flags_ = 0, block_bytes_ = 0;
+  size_t off_recv_x_ = 0, off_meta_ = 0, off_comb_ = 0, off_cnt_ = 0, off_flags_ = 0, off_arrived_ = 0, block_bytes_ = 0;
   void* block_ = nullptr;
   std::vector<char*> bases_;
   std::vector<void*> opened_;
-  torch::Tensor act_, plan_, workspace_, tickets_, status_, by_cta_, pair_slot_, w13_, w2_;
+  torch::Tensor act_, plan_, workspace_, tickets_, status_, by_cta_, pair_slot_, send_pair_, send_target_, w13_, w2_;
   CUtensorMap tm_x_{}, tm_w13_{}, tm_act_{}, tm_w2_{};
   bool ready_ = false, have_weights_ = false;
   uint32_t epoch_ = 0;
@@ -271,7 +286,7 @@ void bind_moe(py::module_& m) {
       .def("close", &MoeEngine::close)
       .def("set_weights", &MoeEngine::set_weights)
       .def("forward", &MoeEngine::forward, py::arg("x"), py::arg("phys_idx"), py::arg("weights"), py::arg("n_cta"),
-           py::arg("upto") = 5)
+           py::arg("upto") = 5, py::arg("fuse_dispatch") = false)
       .def("set_timeout_us", &MoeEngine::set_timeout_us)
       .def("status", &MoeEngine::status)
       .def("plan", &MoeEngine::plan)

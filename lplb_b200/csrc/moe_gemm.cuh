@@ -72,7 +72,54 @@ struct GemmArgs {
   unsigned* ticket;       // zero before launch; left at zero
   int* status;            // first error code
   unsigned long long timeout_ns;
+  // fused dispatch (FUSED kernels only): this rank's rows are sent by warps 6-9 while the
+  // tensor cores work; an expert's tiles start once `arrived[e]` reached `arrive_target[e]`.
+  const __nv_bfloat16* x;        // [tokens, hidden] local hidden states
+  const int* send_pair;          // [n_send] (local expert << 20) | pair index, in send order
+  const int* send_target;        // [n_send] (rank << 24) | row, or -1
+  const int* pair_slot;          // [pairs] return slot of every pair
+  const int* n_send;             // number of send positions
+  const int* arrive_target;      // [n_experts] cumulative rows expected per local expert
+  __nv_bfloat16* recv_x[kMaxRanks];
+  int* recv_meta[kMaxRanks];
+  uint32_t* arrived[kMaxRanks];  // per rank: [n_experts] cumulative rows landed
+  int topk, hidden;
 };
+
+constexpr int kSendWarps = 4;
+constexpr int kFusedThreads = kGemmThreads + 32 * kSendWarps;
+
+// Sender role of the fused kernel: warp `gw` of `n_gw` streams blocks of eight consecutive
+// send positions.  After a block, every lane fences its stores at system scope, the warp
+// re-converges, and one lane per row bumps the target expert's arrival counter on the
+// receiving GPU, which is what the receiver's TMA producer polls.
+__device__ __forceinline__ void send_rows(const GemmArgs& a, int gw, int n_gw, int lane) {
+  const int n_send = *a.n_send;
+  const int vec_per_row = a.hidden / 8;
+  for (int blk = gw; blk * 8 < n_send; blk += n_gw) {
+    const int pos0 = blk * 8, cnt = min(8, n_send - pos0);
+    int my_pair = -1, my_tgt = -1;
+    if (lane < cnt) {
+      my_pair = a.send_pair[pos0 + lane];
+      my_tgt = a.send_target[pos0 + lane];
+    }
+    for (int j = 0; j < cnt; ++j) {
+      const int pr = __shfl_sync(0xffffffffu, my_pair, j), tg = __shfl_sync(0xffffffffu, my_tgt, j);
+      if (tg < 0) continue;
+      const int pair = pr & 0xFFFFF, dr = tg >> 24, row = tg & 0xFFFFFF;
+      const uint4* src = reinterpret_cast<const uint4*>(a.x + (size_t)(pair / a.topk) * a.hidden);
+      uint4* dst = reinterpret_cast<uint4*>(a.recv_x[dr] + (size_t)row * a.hidden);
+      for (int v = lane; v < vec_per_row; v += 32) dst[v] = __ldg(&src[v]);
+      if (lane == 0) a.recv_meta[dr][row] = (a.my_rank << 20) | a.pair_slot[pair];
+    }
+    __threadfence_system();
+    __syncwarp();
+    if (lane < cnt && my_tgt >= 0) {
+      uint32_t* ctr = a.arrived[my_tgt >> 24] + (my_pair >> 20);
+      asm volatile("red.relaxed.sys.global.add.u32 [%0], 1;" ::"l"(ctr) : "memory");
+    }
+  }
+}
 
 struct TileCursor {
   int expert = 0, first_tile = 0;  // first tile id of `expert`
@@ -100,8 +147,8 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
-template <int EPI>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+template <int EPI, bool FUSED = false>
+__global__ void __launch_bounds__(FUSED ? kFusedThreads : kGemmThreads, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                     const GemmArgs args) {
   using namespace sm100;
@@ -167,7 +214,28 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     if (elect_one()) {
       TileCursor cur;
       uint32_t it = 0;  // running k-block counter over all tiles of this CTA
+      int ready_expert = -1;
       for (int t = blockIdx.x; cur.seek(t, args) && !*abort; t += gridDim.x) {
+        if (FUSED && cur.expert != ready_expert) {
+          // all rows of this expert must have landed (senders on every GPU count them in)
+          const uint32_t* ctr = args.arrived[args.my_rank] + cur.expert;
+          const uint32_t want = (uint32_t)args.arrive_target[cur.expert];
+          const uint64_t t0 = timer_ns();
+          for (;;) {
+            uint32_t v;
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(ctr) : "memory");
+            if ((int32_t)(v - want) >= 0) break;
+            if (*abort || timer_ns() - t0 > budget) {
+              *abort = 1;
+              atomicCAS(args.status, 0, kMoeFlagTimeout);
+              break;
+            }
+            __nanosleep(100);
+          }
+          if (*abort) break;
+          fence_proxy_async_global();
+          ready_expert = cur.expert;
+        }
         const int local = t - cur.first_tile;
         const int m = local % cur.tiles_m, n = local / cur.tiles_m;
         const int row_a = args.row_start[cur.expert] + m * kBM;
@@ -216,6 +284,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         umma_commit(bar_tfull + 8 * acc);  // accumulator complete
       }
     }
+  } else if (FUSED && warp >= 6) {
+    // ---------------- senders (never wait on anything) ----------------
+    send_rows(args, blockIdx.x * kSendWarps + (warp - 6), gridDim.x * kSendWarps, lane);
   } else if (go && warp >= 2) {
     // ---------------- epilogue ----------------
     const int quarter = warp & 3;  // TMEM lanes 32*quarter .. +31 are the ones this warp may read

@@ -52,7 +52,7 @@ int make_tensor_map(CUtensorMap* out, const void* base, uint64_t rows, uint64_t 
 }
 
 cudaError_t launch_plan(const LayerShape& sh, const LayerBuffers& b, int n_cta, uint32_t epoch,
-                        unsigned long long timeout_ns, cudaStream_t stream) {
+                        unsigned long long timeout_ns, int fused, cudaStream_t stream) {
   if (!shape_ok(sh) || n_cta < 1) return cudaErrorInvalidValue;
   const int P = sh.n_ranks * sh.n_local;
   PlanArgs a{};
@@ -64,6 +64,7 @@ cudaError_t launch_plan(const LayerShape& sh, const LayerBuffers& b, int n_cta, 
   a.my_rank = sh.my_rank;
   a.n_local = sh.n_local;
   a.capacity = sh.capacity;
+  a.fused = fused;
   a.epoch = epoch;
   a.timeout_ns = timeout_ns;
   plan_kernel<<<1, kSupportThreads, sizeof(int) * 2 * P, stream>>>(a);
@@ -100,6 +101,78 @@ cudaError_t launch_dispatch(const LayerShape& sh, const LayerBuffers& b, const v
   return cudaGetLastError();
 }
 
+namespace {
+int* plan_tail(const LayerShape& sh, const LayerBuffers& b) {
+  const int P = sh.n_ranks * sh.n_local;
+  return b.plan + 2 * sh.n_local + P + sh.n_ranks * P;
+}
+}  // namespace
+
+cudaError_t launch_schedule(const LayerShape& sh, const LayerBuffers& b, const void* phys_idx, int idx_is64,
+                            int n_tokens, int n_cta, cudaStream_t stream) {
+  if (!shape_ok(sh) || n_cta < 1 || n_tokens < 0 || n_tokens > sh.max_tokens) return cudaErrorInvalidValue;
+  const int P = sh.n_ranks * sh.n_local;
+  int* tail = plan_tail(sh, b);
+  ScheduleArgs a{};
+  a.idx = phys_idx;
+  a.by_cta = b.by_cta;
+  a.dst_row_start = b.plan + 2 * sh.n_local;
+  a.order_base = tail + 8;
+  a.send_base = tail + 8 + P;
+  a.pair_slot = b.pair_slot;
+  a.send_pair = b.send_pair;
+  a.send_target = b.send_target;
+  a.n_pairs = (long long)n_tokens * sh.topk;
+  a.idx_is64 = idx_is64;
+  a.n_local = sh.n_local;
+  a.n_ranks = sh.n_ranks;
+  a.capacity = sh.capacity;
+  schedule_kernel<<<n_cta, kSupportThreads, sizeof(int) * P, stream>>>(a);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_dispatch_gemm(const LayerShape& sh, const LayerBuffers& b, const CUtensorMap& tmap_a,
+                                 const CUtensorMap& tmap_b, const void* x, uint32_t epoch,
+                                 unsigned long long timeout_ns, int n_cta, cudaStream_t stream) {
+  if (!shape_ok(sh) || n_cta < 1) return cudaErrorInvalidValue;
+  const int P = sh.n_ranks * sh.n_local;
+  int* tail = plan_tail(sh, b);
+  GemmArgs a{};
+  a.rows = b.plan;
+  a.row_start = b.plan + sh.n_local;
+  a.n_experts = sh.n_local;
+  a.n_ranks = sh.n_ranks;
+  a.my_rank = sh.my_rank;
+  a.epoch = epoch;
+  a.status = b.status;
+  a.timeout_ns = timeout_ns;
+  a.n_tiles_n = 2 * sh.inter / kBN;
+  a.k_blocks = sh.hidden / kBK;
+  a.n_per_expert = 2 * sh.inter;
+  a.act = static_cast<__nv_bfloat16*>(b.act);
+  a.act_ld = sh.inter;
+  a.wait_flags = nullptr;
+  a.ticket = b.tickets + 1;
+  a.x = static_cast<const __nv_bfloat16*>(x);
+  a.send_pair = b.send_pair;
+  a.send_target = b.send_target;
+  a.pair_slot = b.pair_slot;
+  a.n_send = tail + 2;
+  a.arrive_target = tail + 8 + 2 * P;
+  for (int r = 0; r < sh.n_ranks; ++r) {
+    a.recv_x[r] = static_cast<__nv_bfloat16*>(b.recv_x[r]);
+    a.recv_meta[r] = b.recv_meta[r];
+    a.arrived[r] = b.arrived[r];
+  }
+  a.topk = sh.topk;
+  a.hidden = sh.hidden;
+  auto kernel = grouped_gemm_kernel<kSwiGLU, true>;
+  cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kGemmSmem);
+  if (err != cudaSuccess) return err;
+  kernel<<<n_cta, kFusedThreads, kGemmSmem, stream>>>(tmap_a, tmap_b, a);
+  return cudaGetLastError();
+}
+
 cudaError_t launch_gemm(const LayerShape& sh, const LayerBuffers& b, const CUtensorMap& tmap_a,
                         const CUtensorMap& tmap_b, int which, uint32_t epoch, unsigned long long timeout_ns,
                         int n_cta, cudaStream_t stream) {
@@ -122,7 +195,7 @@ cudaError_t launch_gemm(const LayerShape& sh, const LayerBuffers& b, const CUten
     a.act_ld = sh.inter;
     a.wait_flags = b.flags[sh.my_rank];  // dispatch done, one word per source rank
     a.ticket = b.tickets + 1;
-    auto kernel = grouped_gemm_kernel<kSwiGLU>;
+    auto kernel = grouped_gemm_kernel<kSwiGLU, false>;
     err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kGemmSmem);
     if (err != cudaSuccess) return err;
     kernel<<<n_cta, kGemmThreads, kGemmSmem, stream>>>(tmap_a, tmap_b, a);
@@ -138,7 +211,7 @@ cudaError_t launch_gemm(const LayerShape& sh, const LayerBuffers& b, const CUten
     a.out_ld = sh.hidden;
     a.wait_flags = nullptr;
     a.ticket = b.tickets + 2;
-    auto kernel = grouped_gemm_kernel<kScatter>;
+    auto kernel = grouped_gemm_kernel<kScatter, false>;
     err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kGemmSmem);
     if (err != cudaSuccess) return err;
     kernel<<<n_cta, kGemmThreads, kGemmSmem, stream>>>(tmap_a, tmap_b, a);

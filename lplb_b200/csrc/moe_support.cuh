@@ -28,6 +28,7 @@ struct PlanArgs {
   int* plan;                                 // see plan_words() in moe_api.h
   int* status;
   int n_ranks, my_rank, n_local, capacity;
+  int fused;  // the launch uses the fused dispatch: advance the cumulative arrival targets
   uint32_t epoch;
   unsigned long long timeout_ns;
 };
@@ -101,12 +102,82 @@ __global__ void __launch_bounds__(kSupportThreads) plan_kernel(const PlanArgs a)
     for (int s = 0; s < a.my_rank; ++s) before += all_counts[s * P + p];
     dst_row_start[p] = start_all[p] + before;
   }
+  int* order_base = tail + 8;
+  int* send_base = order_base + P;
+  int* arrive_target = send_base + P;
+  int* arrive_cum = arrive_target + a.n_local;
   for (int le = threadIdx.x; le < a.n_local; le += kSupportThreads) {
     // rows past the receive buffer's capacity are dropped by the senders; clamp to match
     const int st = start_all[a.my_rank * a.n_local + le];
     const int n = n_all[a.my_rank * a.n_local + le];
-    rows[le] = max(0, min(n, a.capacity - st));
+    const int kept = max(0, min(n, a.capacity - st));
+    rows[le] = kept;
     row_start[le] = min(st, a.capacity);
+    // the fused dispatch counts landed rows cumulatively over launches
+    const int cum = arrive_cum[le] + (a.fused ? kept : 0);
+    arrive_cum[le] = cum;
+    arrive_target[le] = cum;
+  }
+  if (threadIdx.x == 0) {
+    // Send order of this rank's pairs: local expert index first, then target rank starting
+    // with this rank and rotating, so that at any moment the eight senders aim at eight
+    // different receivers while every rank's expert 0 completes first, then expert 1, ...
+    int pos = 0;
+    for (int le = 0; le < a.n_local; ++le)
+      for (int step = 0; step < a.n_ranks; ++step) {
+        const int p = ((a.my_rank + step) % a.n_ranks) * a.n_local + le;
+        order_base[p] = pos;
+        pos += a.local_counts[p];
+      }
+    tail[2] = pos;
+    int slot = 0;  // return slots: physical expert order
+    for (int p = 0; p < P; ++p) {
+      send_base[p] = slot;
+      slot += a.local_counts[p];
+    }
+  }
+}
+
+struct ScheduleArgs {
+  const void* idx;           // [n_pairs] physical expert ids
+  const int* by_cta;         // [n_cta, P] inclusive prefix rows
+  const int* dst_row_start;  // [P]
+  const int* order_base;     // [P]
+  const int* send_base;      // [P]
+  int* pair_slot;            // [n_pairs] out
+  int* send_pair;            // [n_send] out
+  int* send_target;          // [n_send] out
+  long long n_pairs;
+  int idx_is64, n_local, n_ranks, capacity;
+};
+
+// Same slicing as the counting kernel.  For the k-th pair this rank sends to physical expert e:
+// target row dst_row_start[e] + k, return slot send_base[e] + k, send position order_base[e] + k.
+__global__ void __launch_bounds__(kSupportThreads) schedule_kernel(const ScheduleArgs a) {
+  extern __shared__ int sm[];
+  const int P = a.n_ranks * a.n_local;
+  int* cur = sm;
+  const int p = blockIdx.x, n_cta = gridDim.x;
+  for (int i = threadIdx.x; i < P; i += kSupportThreads) cur[i] = p == 0 ? 0 : a.by_cta[(size_t)(p - 1) * P + i];
+  __syncthreads();
+  const long long begin = slice_begin(a.n_pairs, p, n_cta, kSupportThreads);
+  const long long end = slice_begin(a.n_pairs, p + 1, n_cta, kSupportThreads);
+  for (long long i = begin + threadIdx.x; i < end; i += kSupportThreads) {
+    const long long e = a.idx_is64 ? ((const long long*)a.idx)[i] : (long long)((const int*)a.idx)[i];
+    int slot = -1;
+    if (e >= 0 && e < P) {
+      const int k = atomicAdd(&cur[e], 1);
+      const int row = a.dst_row_start[e] + k;
+      const int pos = a.order_base[e] + k;
+      a.send_pair[pos] = (((int)e % a.n_local) << 20) | (int)i;  // local expert index rides along
+      if (row < a.capacity) {
+        slot = a.send_base[e] + k;
+        a.send_target[pos] = (((int)e / a.n_local) << 24) | row;
+      } else {
+        a.send_target[pos] = -1;
+      }
+    }
+    a.pair_slot[i] = slot;
   }
 }
 

@@ -93,6 +93,7 @@ class MoELayer:
         self.engine.open([bytes(h) for h in handles])
         if group is not None:
             dist.barrier(group=group)
+        self.fuse_dispatch = False
         self._placed_for: torch.Tensor | None = None
         self.place_weights()
 
@@ -136,11 +137,17 @@ class MoELayer:
         raise ValueError(f"unknown routing policy {policy!r}")
 
     # ------------------------------------------------------------------ forward
-    def forward_physical(self, x: torch.Tensor, phys_idx: torch.Tensor, weights: torch.Tensor, upto: int = 5):
+    def forward_physical(
+        self, x: torch.Tensor, phys_idx: torch.Tensor, weights: torch.Tensor, upto: int = 5, fuse_dispatch: bool | None = None
+    ):
+        """Run the layer on physical expert ids.  ``fuse_dispatch`` (default: the layer's
+        setting) sends the rows from inside the first GEMM kernel, so the tensor cores start on
+        an expert as soon as its rows have landed instead of after the whole dispatch."""
         if self._placed_for is None or not torch.equal(self._placed_for, self.planner.phy2log):
             raise RuntimeError("expert placement changed: call place_weights() first")
         n_cta = torch.cuda.get_device_properties(self.device).multi_processor_count
-        return self.engine.forward(x.contiguous(), phys_idx.contiguous(), weights.float().contiguous(), n_cta, upto)
+        fuse = self.fuse_dispatch if fuse_dispatch is None else fuse_dispatch
+        return self.engine.forward(x.contiguous(), phys_idx.contiguous(), weights.float().contiguous(), n_cta, upto, fuse)
 
     def forward(self, x, logical_idx, weights, avail_counter, policy: str = "lplb"):
         return self.forward_physical(x, self.route(logical_idx, avail_counter, policy), weights)

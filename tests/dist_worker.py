@@ -122,6 +122,7 @@ def main():
             mp.update_redundancy_mapping(hist)
             layer.place_weights()
         avail.zero_()
+        layer.fuse_dispatch = step >= 2  # later steps send the rows from inside the first GEMM
         out = layer.forward(x, idx, w, avail, "lplb" if step % 2 == 0 else "static")
         torch.cuda.synchronize(dev)
         assert layer.check() == 0, layer.engine.status().tolist()

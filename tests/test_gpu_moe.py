@@ -76,12 +76,14 @@ def test_layer_matches_fp32_reference(hidden, inter, tokens, topk):
     layer.place_weights()
     avail = torch.zeros(1, dtype=torch.int32, device="cuda")
     ref = layer.reference_forward(x, idx, w).float()
-    for policy in ("lplb", "static"):
+    for policy, fuse in (("lplb", False), ("static", False), ("lplb", True), ("static", True), ("lplb", False)):
+        layer.fuse_dispatch = fuse  # True: rows are sent from inside the first GEMM kernel
         out = layer.forward(x, idx, w, avail, policy)
         torch.cuda.synchronize()
         assert layer.check() == 0
         err = (out.float() - ref).abs().max() / ref.abs().max()
-        assert float(err) < 2e-2, (policy, float(err))
+        assert float(err) < 2e-2, (policy, fuse, float(err))
+    layer.fuse_dispatch = False
     # the first GEMM alone, row by row, against silu(x Wg^T) * (x Wu^T)
     phys = layer.route(idx, avail, "lplb")
     layer.forward_physical(x, phys, w, upto=3)
