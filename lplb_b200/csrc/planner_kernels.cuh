@@ -56,9 +56,10 @@ __device__ __forceinline__ int* ws_global(Workspace* ws, int e) { return reinter
 // ignored and counted in the status block.
 template <typename IdxT>
 __device__ __forceinline__ void histogram_slice(const IdxT* __restrict__ idx, long long begin, long long end, int e,
-                                                int* __restrict__ hist, int* status) {
+                                                int* __restrict__ hist, int* status, int tid = threadIdx.x,
+                                                int stride = kBlock) {
   int bad = 0;
-  for (long long i = begin + threadIdx.x; i < end; i += kBlock) {
+  for (long long i = begin + tid; i < end; i += stride) {
     const long long v = (long long)idx[i];
     if (v >= 0 && v < e) atomicAdd(&hist[v], 1);
     else if (v != -1) ++bad;
@@ -392,7 +393,25 @@ __global__ void __launch_bounds__(kBlock) fused_run_kernel(const IdxT* __restric
   int* total_g = ws_total(ws, parity, e);
 
   const long long begin = slice_begin(n, p, n_cta, kBlock), end = slice_begin(n, p + 1, n_cta, kBlock);
-  histogram_slice(idx, begin, end, e, hist, status);
+  if (p == 0) {
+    // CTA 0 will run the LP: start fetching the tables it gathers from, in the shadow of the
+    // counting phase (they were evicted if anything ran since the last step).
+    const int n_slots = tp.n_group * tp.g * tp.pl;
+    for (int i = threadIdx.x * 32; i < n_slots; i += kBlock * 32)
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(tp.phy2log + i));
+    if (threadIdx.x == 0) {
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(tp.r2o));
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(tp.o2r));
+    }
+    histogram_slice(idx, begin, end, e, hist, status);
+  } else {
+    histogram_slice(idx, begin, end, e, hist, status);
+    // static lookup tables, fetched while CTA 0 works (quota[] holds the edge ids for now)
+    for (int i = threadIdx.x; i < e; i += kBlock) {
+      quota[i] = tp.log2edge[i];
+      phys[i] = reinterpret_cast<const int2*>(tp.log2phy)[i];
+    }
+  }
   __syncthreads();
   for (int i = threadIdx.x; i < e; i += kBlock) {
     const int c = hist[i];
@@ -454,9 +473,9 @@ __global__ void __launch_bounds__(kBlock) fused_run_kernel(const IdxT* __restric
   for (int i = threadIdx.x; i < e; i += kBlock) {
     const int tot = __ldcg(&total_g[i]);
     hist[i] = tot;
-    const int edge = tp.log2edge[i];
+    const int edge = p == 0 ? tp.log2edge[i] : quota[i];
     quota[i] = have_probs ? quota_of(tot, edge, probs) : (edge < 0 ? tot : tot / 2);
-    phys[i] = reinterpret_cast<const int2*>(tp.log2phy)[i];
+    if (p == 0) phys[i] = reinterpret_cast<const int2*>(tp.log2phy)[i];
   }
   __syncthreads();
   redirect_slice(idx, begin, end, e, cur, hist, quota, phys, out);
