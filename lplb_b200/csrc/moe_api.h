@@ -40,6 +40,7 @@ struct LayerBuffers {
   int* send_pair;                      // int32 [max_tokens * topk] pair index at every send position
   int* send_target;                    // int32 [max_tokens * topk] (rank << 24) | row, or -1
   uint32_t* arrived[kApiMaxRanks];     // per rank: uint32 [n_local] rows that have landed, cumulative
+  unsigned long long* debug;           // optional uint64 [n_cta * 4] timing of the fused kernel, may be null
   void* planner_workspace;             // counting kernel workspace (ticket)
   unsigned* tickets;                   // uint32 [4], zero
   int* status;                         // int32 [16]

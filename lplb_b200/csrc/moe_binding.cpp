@@ -214,6 +214,19 @@ class MoeEngine {
   torch::Tensor plan() const { return plan_; }
   torch::Tensor act() const { return act_; }
   torch::Tensor pair_slot() const { return pair_slot_; }
+  // Timing of the fused dispatch+GEMM kernel, [n_sm, 4] ns per CTA: start, senders done,
+  // time the TMA producer spent waiting for rows, end.  Zeroed on enable.
+  torch::Tensor enable_debug(bool on) {
+    c10::cuda::CUDAGuard guard(device_);
+    if (on) {
+      debug_ = torch::zeros({sm_count(), 4}, torch::TensorOptions().dtype(torch::kInt64).device(torch::kCUDA, device_));
+      buf_.debug = reinterpret_cast<unsigned long long*>(debug_.data_ptr());
+    } else {
+      debug_ = torch::Tensor();
+      buf_.debug = nullptr;
+    }
+    return debug_;
+  }
   int64_t epoch() const { return epoch_; }
 
   // Views of this rank's peer-visible buffers (for tests).
@@ -250,6 +263,7 @@ class MoeEngine {
     buf_.act = act_.data_ptr();
     buf_.plan = plan_.data_ptr<int>();
     buf_.by_cta = nullptr;
+    buf_.debug = nullptr;
     buf_.pair_slot = pair_slot_.data_ptr<int>();
     buf_.send_pair = send_pair_.data_ptr<int>();
     buf_.send_target = send_target_.data_ptr<int>();
@@ -266,7 +280,7 @@ class MoeEngine {
   void* block_ = nullptr;
   std::vector<char*> bases_;
   std::vector<void*> opened_;
-  torch::Tensor act_, plan_, workspace_, tickets_, status_, by_cta_, pair_slot_, send_pair_, send_target_, w13_, w2_;
+  torch::Tensor act_, plan_, workspace_, tickets_, status_, by_cta_, pair_slot_, send_pair_, send_target_, debug_, w13_, w2_;
   CUtensorMap tm_x_{}, tm_w13_{}, tm_act_{}, tm_w2_{};
   bool ready_ = false, have_weights_ = false;
   uint32_t epoch_ = 0;
@@ -292,6 +306,7 @@ void bind_moe(py::module_& m) {
       .def("plan", &MoeEngine::plan)
       .def("act", &MoeEngine::act)
       .def("pair_slot", &MoeEngine::pair_slot)
+      .def("enable_debug", &MoeEngine::enable_debug)
       .def("epoch", &MoeEngine::epoch)
       .def("recv_x", &MoeEngine::recv_x)
       .def("recv_meta", &MoeEngine::recv_meta)

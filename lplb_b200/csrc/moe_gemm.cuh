@@ -84,6 +84,7 @@ struct GemmArgs {
   int* recv_meta[kMaxRanks];
   uint32_t* arrived[kMaxRanks];  // per rank: [n_experts] cumulative rows landed
   int topk, hidden;
+  unsigned long long* debug;     // optional [gridDim.x * 4] ns: kernel start, senders done, producer wait, end
 };
 
 constexpr int kSendWarps = 4;
@@ -109,7 +110,15 @@ __device__ __forceinline__ void send_rows(const GemmArgs& a, int gw, int n_gw, i
       const int pair = pr & 0xFFFFF, dr = tg >> 24, row = tg & 0xFFFFFF;
       const uint4* src = reinterpret_cast<const uint4*>(a.x + (size_t)(pair / a.topk) * a.hidden);
       uint4* dst = reinterpret_cast<uint4*>(a.recv_x[dr] + (size_t)row * a.hidden);
-      for (int v = lane; v < vec_per_row; v += 32) dst[v] = __ldg(&src[v]);
+      int v = lane;
+      for (; v + 96 < vec_per_row; v += 128) {  // four independent 16-byte loads in flight per lane
+        const uint4 q0 = __ldg(&src[v]), q1 = __ldg(&src[v + 32]), q2 = __ldg(&src[v + 64]), q3 = __ldg(&src[v + 96]);
+        dst[v] = q0;
+        dst[v + 32] = q1;
+        dst[v + 64] = q2;
+        dst[v + 96] = q3;
+      }
+      for (; v < vec_per_row; v += 32) dst[v] = __ldg(&src[v]);
       if (lane == 0) a.recv_meta[dr][row] = (a.my_rank << 20) | a.pair_slot[pair];
     }
     __threadfence_system();
@@ -167,8 +176,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   __shared__ int s_flags_ok;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  unsigned long long* dbg = FUSED && args.debug ? args.debug + 4 * blockIdx.x : nullptr;
 
   if (threadIdx.x == 0) {
+    if (dbg) dbg[0] = timer_ns();
     abort_flag = 0;
     s_flags_ok = 1;
     for (int s = 0; s < kStages; ++s) {
@@ -232,6 +243,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             }
             __nanosleep(100);
           }
+          if (dbg) dbg[2] += timer_ns() - t0;
           if (*abort) break;
           fence_proxy_async_global();
           ready_expert = cur.expert;
@@ -287,6 +299,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   } else if (FUSED && warp >= 6) {
     // ---------------- senders (never wait on anything) ----------------
     send_rows(args, blockIdx.x * kSendWarps + (warp - 6), gridDim.x * kSendWarps, lane);
+    if (dbg && lane == 0) atomicMax(&dbg[1], (unsigned long long)timer_ns());
   } else if (go && warp >= 2) {
     // ---------------- epilogue ----------------
     const int quarter = warp & 3;  // TMEM lanes 32*quarter .. +31 are the ones this warp may read
@@ -385,6 +398,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   tc_fence_before_sync();
   __syncthreads();
   if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
+  if (dbg && threadIdx.x == 0) dbg[3] = timer_ns();
   if (threadIdx.x == 0 && args.ticket != nullptr) {
     __threadfence();
     if (atomicAdd(args.ticket, 1u) == gridDim.x - 1) {

@@ -166,6 +166,7 @@ cudaError_t launch_dispatch_gemm(const LayerShape& sh, const LayerBuffers& b, co
   }
   a.topk = sh.topk;
   a.hidden = sh.hidden;
+  a.debug = b.debug;
   auto kernel = grouped_gemm_kernel<kSwiGLU, true>;
   cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kGemmSmem);
   if (err != cudaSuccess) return err;
