@@ -295,3 +295,16 @@ def test_exchange_wait_runs_out_and_falls_back():
     assert torch.allclose(local.last_probs, eng.last_probs(), atol=1e-6)
     # the context is still healthy
     assert int(torch.ones(4, device="cuda").sum()) == 4
+
+
+# ---------------------------------------------------------------- timing helpers
+def test_timing_helpers_report_the_solve_kernel():
+    from lplb_b200.utils.timing import bench_kineto, time_cuda
+
+    planner = _planner(topology.cube(), 64, 8, 2)
+    _, current = synthetic_loads(64, seed=1, device="cuda")
+    avail = torch.zeros((), dtype=torch.int32, device="cuda")
+    seconds = bench_kineto(lambda: planner.solve_probs(current, avail), "solve_kernel", 20)
+    assert 1e-6 < seconds < 1e-3
+    stats = time_cuda(lambda: planner.solve_probs(current, avail), iters=20, warmup=3)
+    assert stats["min"] <= stats["p50"] <= stats["max"] and stats["p50"] < 1e3
