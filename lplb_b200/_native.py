@@ -23,7 +23,9 @@ log = logging.getLogger("lplb_b200")
 
 _ROOT = Path(__file__).resolve().parent
 _CSRC = _ROOT / "csrc"
-_BUILD = _ROOT / "_build"
+# Where the binary and its fingerprint live.  LPLB_B200_CACHE_PATH relocates it (the
+# reference's LPLB_CACHE_PATH does the same for its JIT cache, reference csrc/plugin.cpp:207-214).
+_BUILD = Path(os.environ["LPLB_B200_CACHE_PATH"]) if os.environ.get("LPLB_B200_CACHE_PATH") else _ROOT / "_build"
 _NAME = "lplb_b200_native"
 
 SOURCES = [

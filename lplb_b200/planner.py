@@ -25,7 +25,9 @@ Differences that a user can observe, all deliberate:
 
 from __future__ import annotations
 
+import contextlib
 import logging
+import os
 from typing import Any
 
 import torch
@@ -314,11 +316,12 @@ class Planner:
         (reference ``lplb/planner.py:245-266``)."""
         if n_sms is None:
             n_sms = self._default_sms()
-        if self._engine is not None and self.comm in ("p2p", "none"):
-            return self._engine.run_fused(idx.contiguous(), avail_counter, int(n_sms), self.comm == "p2p")
-        local, by_sm = self.count_workload(idx, n_sms)
-        probs, _ = self.solve_probs(local, avail_counter)
-        return self.weighted_select_target(idx, probs, by_sm, n_sms)
+        with self._nvtx("lplb_b200.planner.run"):
+            if self._engine is not None and self.comm in ("p2p", "none"):
+                return self._engine.run_fused(idx.contiguous(), avail_counter, int(n_sms), self.comm == "p2p")
+            local, by_sm = self.count_workload(idx, n_sms)
+            probs, _ = self.solve_probs(local, avail_counter)
+            return self.weighted_select_target(idx, probs, by_sm, n_sms)
 
     def run_staged(self, idx: torch.Tensor, avail_counter: torch.Tensor, n_sms: int | None = None) -> torch.Tensor:
         """The three-launch pipeline regardless of ``comm`` (baseline for measurements)."""
@@ -352,6 +355,33 @@ class Planner:
         if clear:
             self._engine.status().zero_()
         return out
+
+    def _nvtx(self, name: str):
+        """NVTX range around the hot path when LPLB_B200_NVTX=1 (for timeline profilers)."""
+        if self._engine is not None and os.environ.get("LPLB_B200_NVTX") == "1":
+            return torch.cuda.nvtx.range(name)
+        return contextlib.nullcontext()
+
+    def dump_lp(self, workload: torch.Tensor) -> dict[str, Any]:
+        """Everything the solver sees for the given (already summed) statistics, on the host:
+        bundle loads, fixed loads, the compact form ``M, base`` and the equality form
+        ``A, b, c`` of every group, plus the float64 oracle's shares and optimum.  This is the
+        inspectable counterpart of the reference's compile-time ``DEBUG_DUMP`` printf of
+        ``A``, ``b``, ``c`` and ``x`` (reference ``lplb/resources/csrc-tmpl/minilp.cu:295-321``)."""
+        wl = workload.detach().reshape(-1).to("cpu", torch.float64)
+        r2o = self.r2o.cpu()
+        w, fixed = _lp.bundle_loads(
+            wl, self.phy2log.cpu(), self.n_group, self.group_size, self.num_redundants,
+            self.n_local_logical_routed_experts, self.combined_redundant_experts,
+        )
+        m, base = _lp.compact_form(w, fixed, r2o)
+        oracle = _lp.solve_ipm(w, fixed, r2o, tol=1e-9, max_iters=60)
+        standard = [_lp.standard_form(w[g], fixed[g], r2o) for g in range(self.n_group)]
+        return {
+            "bundle_loads": w, "fixed_loads": fixed, "M": m, "base": base,
+            "A": [t[0] for t in standard], "b": [t[1] for t in standard], "c": [t[2] for t in standard],
+            "oracle_shares": oracle.f, "oracle_max_load": oracle.t, "oracle_iterations": oracle.iters,
+        }
 
     def enable_trace(self, on: bool = True) -> None:
         """Make the fused kernel write per-phase ``globaltimer`` stamps (a few extra stores)."""

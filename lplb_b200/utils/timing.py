@@ -9,12 +9,34 @@ reads the kernel times from the profiler's event list instead of parsing its tex
 
 from __future__ import annotations
 
+import contextlib
+import os
 import statistics
+import sys
 from typing import Callable, Sequence
 
 import torch
 
-__all__ = ["L2Flusher", "time_cuda", "bench_kineto"]
+__all__ = ["L2Flusher", "time_cuda", "bench_kineto", "suppress_output"]
+
+
+@contextlib.contextmanager
+def suppress_output():
+    """Silence stdout and stderr at the file-descriptor level (profiler chatter included),
+    like the helper in the reference's test utilities (reference ``tests/utils.py:16-43``)."""
+    sys.stdout.flush()
+    sys.stderr.flush()
+    saved = os.dup(1), os.dup(2)
+    with open(os.devnull, "w") as null:
+        os.dup2(null.fileno(), 1)
+        os.dup2(null.fileno(), 2)
+        try:
+            yield
+        finally:
+            os.dup2(saved[0], 1)
+            os.dup2(saved[1], 2)
+            os.close(saved[0])
+            os.close(saved[1])
 
 
 class L2Flusher:

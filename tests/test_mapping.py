@@ -75,3 +75,15 @@ def test_constructor_validation():
         Planner(topology.cube(), 80, 64, 12, device="cpu")
     with pytest.raises(ValueError):
         Planner(topology.cube(), 72, 64, 8, device="cpu")  # 1 redundant per rank cannot fill 2 slots
+
+
+def test_dump_lp_exposes_the_solver_inputs():
+    from lplb_b200 import lp
+
+    p = Planner(topology.cube(), 80, 64, 8, device="cpu")
+    wl = torch.arange(64) * 3 + 5
+    d = p.dump_lp(wl)
+    assert d["M"].shape == (1, 8, 16) and d["A"][0].shape == (24, 42)
+    assert torch.allclose(d["M"].sum(1), torch.zeros(1, 16, dtype=torch.float64))  # columns sum to zero
+    _, t_opt = lp.solve_highs(d["bundle_loads"][0], d["fixed_loads"][0], topology.cube())
+    assert abs(float(d["oracle_max_load"][0]) - t_opt) / t_opt < 1e-6
