@@ -159,9 +159,20 @@ class PlannerEngine {
   }
 
   // ---- single launch ------------------------------------------------------------------
-  torch::Tensor run_fused(const torch::Tensor& idx, torch::Tensor avail, int n_cta, bool use_exchange) {
+  // `idx` may also be a pinned host tensor: the kernel then reads it over PCIe itself and,
+  // if `out` is a pinned host tensor too, writes the result straight back, which replaces two
+  // copy-engine transfers and their launch latencies.  `out` must match `idx` in shape/dtype.
+  torch::Tensor run_fused(const torch::Tensor& idx, torch::Tensor avail, int n_cta, bool use_exchange,
+                          c10::optional<torch::Tensor> out_opt) {
     require_mapping();
-    check_idx(idx);
+    const bool host_idx = !idx.is_cuda();
+    if (host_idx) {
+      LPLB_CHECK(idx.is_pinned(), "host indices must be in pinned memory");
+      LPLB_CHECK(idx.scalar_type() == torch::kInt64 || idx.scalar_type() == torch::kInt32, "indices must be int64 or int32");
+      LPLB_CHECK(idx.is_contiguous(), "indices must be contiguous");
+    } else {
+      check_idx(idx);
+    }
     check_avail(avail);
     c10::cuda::CUDAGuard guard(device_);
     const int is64 = idx.scalar_type() == torch::kInt64;
@@ -169,7 +180,17 @@ class PlannerEngine {
     if (limit < 0) limit = lplb::max_fused_ctas(g_, d_, e_, is64);
     LPLB_CHECK(limit > 0, "fused kernel cannot be resident on this device");
     if (n_cta > limit) n_cta = limit;
-    auto out = torch::empty_like(idx);
+    torch::Tensor out;
+    if (out_opt.has_value()) {
+      out = *out_opt;
+      LPLB_CHECK(out.sizes() == idx.sizes() && out.scalar_type() == idx.scalar_type() && out.is_contiguous(),
+                 "out must match idx in shape and dtype and be contiguous");
+      LPLB_CHECK((out.is_cuda() && out.get_device() == device_) || (!out.is_cuda() && out.is_pinned()),
+                 "out must live on this device or in pinned host memory");
+    } else {
+      LPLB_CHECK(!host_idx, "pass a pinned `out` tensor together with pinned host indices");
+      out = torch::empty_like(idx);
+    }
     lplb::ExchangeDesc ex{nullptr, 1, 0, peer_timeout_ns_};
     if (use_exchange) {
       LPLB_CHECK(exchange_open_, "exchange buffers are not open; call open_exchange first");
@@ -368,7 +389,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def("count_idx", &PlannerEngine::count_idx)
       .def("solve", &PlannerEngine::solve)
       .def("map_idx", &PlannerEngine::map_idx)
-      .def("run_fused", &PlannerEngine::run_fused)
+      .def("run_fused", &PlannerEngine::run_fused, py::arg("idx"), py::arg("avail"), py::arg("n_cta"),
+           py::arg("use_exchange"), py::arg("out") = py::none())
       .def("all_reduce_counts", &PlannerEngine::all_reduce_counts)
       .def("alloc_exchange", &PlannerEngine::alloc_exchange)
       .def("open_exchange", &PlannerEngine::open_exchange)

@@ -111,6 +111,67 @@ __device__ __forceinline__ void redirect_slice(const IdxT* __restrict__ idx, lon
   }
 }
 
+// The fused kernel touches every index twice (count, then rewrite).  Each thread keeps its
+// first kKeep indices in registers between the two phases, so the index array is read from
+// memory once; that matters most when the array lives in pinned host memory and every read
+// crosses PCIe.  Loads are cache-volatile so a host buffer that is refilled between launches
+// is never served stale.
+constexpr int kKeep = 4;
+
+template <typename IdxT>
+__device__ __forceinline__ long long load_index(const IdxT* p) {
+  return (long long)__ldcv(p);
+}
+
+template <typename IdxT>
+__device__ __forceinline__ void histogram_keep(const IdxT* __restrict__ idx, long long begin, long long end, int e,
+                                               int* __restrict__ hist, int* status, long long (&keep)[kKeep]) {
+  int bad = 0;
+#pragma unroll
+  for (int j = 0; j < kKeep; ++j) {
+    const long long i = begin + threadIdx.x + (long long)j * kBlock;
+    keep[j] = -1;
+    if (i < end) {
+      const long long v = load_index(idx + i);
+      keep[j] = v;
+      if (v >= 0 && v < e) atomicAdd(&hist[v], 1);
+      else if (v != -1) ++bad;
+    }
+  }
+  for (long long i = begin + threadIdx.x + (long long)kKeep * kBlock; i < end; i += kBlock) {
+    const long long v = load_index(idx + i);
+    if (v >= 0 && v < e) atomicAdd(&hist[v], 1);
+    else if (v != -1) ++bad;
+  }
+  if (bad) {
+    atomicAdd(&status[kStBadIdx], bad);
+    raise_status(status, kErrBadIndex, kPhCount, bad);
+  }
+}
+
+template <typename IdxT>
+__device__ __forceinline__ void redirect_keep(const IdxT* __restrict__ idx, long long begin, long long end, int e,
+                                              int* __restrict__ cur, const int* __restrict__ total,
+                                              const int* __restrict__ quota, const int2* __restrict__ phys,
+                                              IdxT* __restrict__ out, const long long (&keep)[kKeep]) {
+  auto place = [&](long long i, long long v) {
+    long long o = -1;
+    if (v >= 0 && v < e) {
+      const int2 ph = phys[v];
+      const int k = atomicAdd(&cur[v], 1);
+      const bool stay = ph.y < 0 || even_pick((unsigned)k, (unsigned)quota[v], (unsigned)total[v]);
+      o = stay ? ph.x : ph.y;
+    }
+    out[i] = (IdxT)o;
+  };
+#pragma unroll
+  for (int j = 0; j < kKeep; ++j) {
+    const long long i = begin + threadIdx.x + (long long)j * kBlock;
+    if (i < end) place(i, keep[j]);
+  }
+  for (long long i = begin + threadIdx.x + (long long)kKeep * kBlock; i < end; i += kBlock) place(i, load_index(idx + i));
+}
+
 // ---------------------------------------------------------------------------------------
 // Stand-alone counting kernel.  Row p of `by_cta` receives CTA p's counts; the CTA that
 // finishes last turns the rows into inclusive prefixes over CTAs, so row n_cta-1 is the
@@ -393,6 +454,7 @@ __global__ void __launch_bounds__(kBlock) fused_run_kernel(const IdxT* __restric
   int* total_g = ws_total(ws, parity, e);
 
   const long long begin = slice_begin(n, p, n_cta, kBlock), end = slice_begin(n, p + 1, n_cta, kBlock);
+  long long keep[kKeep];
   if (p == 0) {
     // CTA 0 will run the LP: start fetching the tables it gathers from, in the shadow of the
     // counting phase (they were evicted if anything ran since the last step).
@@ -403,9 +465,9 @@ __global__ void __launch_bounds__(kBlock) fused_run_kernel(const IdxT* __restric
       asm volatile("prefetch.global.L2 [%0];" ::"l"(tp.r2o));
       asm volatile("prefetch.global.L2 [%0];" ::"l"(tp.o2r));
     }
-    histogram_slice(idx, begin, end, e, hist, status);
+    histogram_keep(idx, begin, end, e, hist, status, keep);
   } else {
-    histogram_slice(idx, begin, end, e, hist, status);
+    histogram_keep(idx, begin, end, e, hist, status, keep);
     // static lookup tables, fetched while CTA 0 works (quota[] holds the edge ids for now)
     for (int i = threadIdx.x; i < e; i += kBlock) {
       quota[i] = tp.log2edge[i];
@@ -478,7 +540,7 @@ __global__ void __launch_bounds__(kBlock) fused_run_kernel(const IdxT* __restric
     if (p == 0) phys[i] = reinterpret_cast<const int2*>(tp.log2phy)[i];
   }
   __syncthreads();
-  redirect_slice(idx, begin, end, e, cur, hist, quota, phys, out);
+  redirect_keep(idx, begin, end, e, cur, hist, quota, phys, out, keep);
 
   __syncthreads();
   if (tracing && p == 0) trace[5] = global_timer_ns();

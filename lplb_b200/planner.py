@@ -138,6 +138,7 @@ class Planner:
         self.ep_group = group
         self.deep_ep_initialized = False  # name kept from the reference: "in-kernel exchange is live"
         self._n_sms_default: int | None = None
+        self._host_out: tuple | None = None
 
         self._engine = None
         if self.device.type == "cuda":
@@ -311,17 +312,41 @@ class Planner:
         return _ref.redirect_reference(idx, o_weight, self.mapping.log2phy, self.mapping.log2edge)
 
     # ------------------------------------------------------------------ hot path
-    def run(self, idx: torch.Tensor, avail_counter: torch.Tensor, n_sms: int | None = None) -> torch.Tensor:
+    def run(
+        self,
+        idx: torch.Tensor,
+        avail_counter: torch.Tensor,
+        n_sms: int | None = None,
+        out: torch.Tensor | None = None,
+    ) -> torch.Tensor:
         """Logical expert ids ``[-1, E)`` in, physical expert ids ``[-1, P)`` out, same shape
-        (reference ``lplb/planner.py:245-266``)."""
+        (reference ``lplb/planner.py:245-266``).
+
+        ``idx`` normally lives on the planner's GPU.  It may instead be a *pinned host* tensor:
+        the kernel then reads it over PCIe itself (no separate host-to-device copy), and the
+        result is written to ``out``, which may be a pinned host tensor as well (no separate
+        device-to-host copy).  Without ``out`` a pinned buffer cached on the planner is
+        returned; it is overwritten by the next such call.  The caller synchronises the stream
+        before reading a host result."""
         if n_sms is None:
             n_sms = self._default_sms()
         with self._nvtx("lplb_b200.planner.run"):
             if self._engine is not None and self.comm in ("p2p", "none"):
-                return self._engine.run_fused(idx.contiguous(), avail_counter, int(n_sms), self.comm == "p2p")
+                if not idx.is_cuda and out is None:
+                    key = (tuple(idx.shape), idx.dtype)
+                    if self._host_out is None or self._host_out[0] != key:
+                        self._host_out = (key, torch.empty(idx.shape, dtype=idx.dtype).pin_memory())
+                    out = self._host_out[1]
+                return self._engine.run_fused(idx.contiguous(), avail_counter, int(n_sms), self.comm == "p2p", out)
+            if not idx.is_cuda and self._engine is not None:
+                idx = idx.to(self.device, non_blocking=True)
             local, by_sm = self.count_workload(idx, n_sms)
             probs, _ = self.solve_probs(local, avail_counter)
-            return self.weighted_select_target(idx, probs, by_sm, n_sms)
+            res = self.weighted_select_target(idx, probs, by_sm, n_sms)
+            if out is not None:
+                out.copy_(res, non_blocking=True)
+                return out
+            return res
 
     def run_staged(self, idx: torch.Tensor, avail_counter: torch.Tensor, n_sms: int | None = None) -> torch.Tensor:
         """The three-launch pipeline regardless of ``comm`` (baseline for measurements)."""

@@ -252,6 +252,32 @@ def test_fused_run_balances_real_routing():
     assert float(after.max()) <= t_opt * (1 + 1e-3) + 16
 
 
+def test_run_reads_and_writes_pinned_host_memory():
+    planner = _planner(topology.cube(), 256, 8, 2)
+    gen = torch.Generator("cuda").manual_seed(3)
+    avail = torch.zeros(1, dtype=torch.int32, device="cuda")
+    for n_tokens, n_sms in ((4096, _sms()), (300, 5), (40000, 16)):  # the last one exceeds the register-kept part
+        idx = (torch.randn(n_tokens, 256, device="cuda", generator=gen)).topk(8, dim=-1).indices
+        idx[::11, 2] = -1
+        host_idx = idx.cpu().pin_memory()
+        host_out = torch.empty_like(host_idx).pin_memory()
+        got = planner.run(host_idx, avail, n_sms, out=host_out)
+        torch.cuda.synchronize()
+        assert got.data_ptr() == host_out.data_ptr() and not got.is_cuda
+        _check_redirect(planner, idx, host_out.cuda(), planner.last_probs)
+        # same shares and quotas as the all-device call
+        dev_out = planner.run(idx, avail, n_sms)
+        assert torch.equal(torch.bincount(dev_out.reshape(-1) + 1, minlength=273).cpu(),
+                           torch.bincount(host_out.reshape(-1) + 1, minlength=273))
+        # device result written into a caller-provided device buffer
+        buf = torch.empty_like(idx)
+        assert planner.run(idx, avail, n_sms, out=buf).data_ptr() == buf.data_ptr()
+    cached = planner.run(host_idx, avail)
+    torch.cuda.synchronize()
+    assert cached.is_pinned() and cached.shape == host_idx.shape
+    assert planner.check_status().ok
+
+
 # ---------------------------------------------------------------- exchange on one GPU
 def test_exchange_loopback_sums_prefilled_peer():
     planner = _planner(topology.cube(), 64, 8, 2)
