@@ -206,9 +206,10 @@ __global__ void __launch_bounds__(kBlock) count_kernel(const IdxT* __restrict__ 
 }
 
 // ---------------------------------------------------------------------------------------
-// LP phase shared by the stand-alone solve kernel and the fused kernel.  `cnt` holds the
-// group-wide (already summed over ranks) counts per logical expert, in shared or global
-// memory.  Each warp carries 32/GP groups; a CTA covers `kWarps * 32/GP` groups per round.
+// LP phase shared by the stand-alone solve kernel and the fused kernel.  `bundle` holds the
+// per-rank bundle and fixed loads made by bundle_sums from the group-wide (already summed
+// over ranks) counts.  Each warp carries 32/GP groups; a CTA covers `kWarps * 32/GP` groups
+// per round.
 // The success counter may be an int32 or an int64 tensor (the reference's README shows
 // int64, its launcher demands int32: reference README.md:32, csrc/plugin.cpp:528-529).
 struct Counter {
@@ -220,8 +221,28 @@ __device__ __forceinline__ void bump(Counter c) {
   else atomicAdd(reinterpret_cast<int*>(c.ptr), 1);
 }
 
+// Whole-CTA prologue of the LP: fold the per-expert counts into per-rank bundle loads with one
+// load per (rank, slot) spread over all threads, instead of a serial walk by the few lanes that
+// solve.  bundle[rank * (D + 1) + d] = load of the rank's bundle d, [.. + D] = its fixed load.
+// Integer sums, so the result does not depend on the order of the atomics.
+// Only ranks [rank_begin, rank_end) are filled (a CTA of the stand-alone kernel needs its own
+// groups only); `bundle` is indexed by absolute rank.
+template <int D>
+__device__ __forceinline__ void bundle_sums(const int* __restrict__ cnt, const Topo& tp, int* __restrict__ bundle,
+                                            int rank_begin, int rank_end) {
+  const int n_rep = tp.c * D;
+  for (int i = rank_begin * (D + 1) + threadIdx.x; i < rank_end * (D + 1); i += kBlock) bundle[i] = 0;
+  __syncthreads();
+  for (int i = rank_begin * tp.ll + threadIdx.x; i < rank_end * tp.ll; i += kBlock) {
+    const int rank = i / tp.ll, sl = i - rank * tp.ll;
+    const int c = cnt[tp.phy2log[(size_t)rank * tp.pl + sl]];
+    if (c) atomicAdd(&bundle[rank * (D + 1) + (sl < n_rep ? sl % D : D)], c);
+  }
+  __syncthreads();
+}
+
 template <int GP, int D>
-__device__ void solve_groups(const int* __restrict__ cnt, const Topo& tp, int first_group, int group_stride,
+__device__ void solve_groups(const int* __restrict__ bundle, const Topo& tp, int first_group, int group_stride,
                              IpmParams prm, float* __restrict__ probs, Counter avail, int* status) {
   constexpr int kSeg = 32 / GP;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -237,17 +258,11 @@ __device__ void solve_groups(const int* __restrict__ cnt, const Topo& tp, int fi
       src[d] = dst[d] = li;
     }
     if (live) {
-      const int* slots = tp.phy2log + ((size_t)grp * tp.g + li) * tp.pl;
-      const int n_rep = tp.c * D;
-      for (int sl = 0; sl < n_rep; ++sl) {
-        const double x = (double)cnt[slots[sl]];
-#pragma unroll
-        for (int d = 0; d < D; ++d)
-          if (sl % D == d) w[d] += x;
-      }
-      for (int sl = n_rep; sl < tp.ll; ++sl) fixed += (double)cnt[slots[sl]];
+      const int* mine = bundle + ((size_t)grp * tp.g + li) * (D + 1);
+      fixed = (double)mine[D];
 #pragma unroll
       for (int d = 0; d < D; ++d) {
+        w[d] = (double)mine[d];
         src[d] = tp.r2o[li * D + d];
         dst[d] = tp.o2r[li * D + d];
       }
@@ -290,8 +305,11 @@ __global__ void __launch_bounds__(kBlock) solve_kernel(const int* __restrict__ w
     if (threadIdx.x == 0) status[kStLpIters] = 0;
     __syncthreads();
   }
+  extern __shared__ int bundle[];
   constexpr int kPerCta = kWarps * (32 / GP);
-  solve_groups<GP, D>(workload, tp, blockIdx.x * kPerCta, gridDim.x * kPerCta, prm, probs, avail, status);
+  bundle_sums<D>(workload, tp, bundle, min(tp.n_group, (int)blockIdx.x * kPerCta) * tp.g,
+                 min(tp.n_group, ((int)blockIdx.x + 1) * kPerCta) * tp.g);
+  solve_groups<GP, D>(bundle, tp, blockIdx.x * kPerCta, gridDim.x * kPerCta, prm, probs, avail, status);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -425,7 +443,8 @@ __global__ void __launch_bounds__(kBlock) exchange_kernel(const int* __restrict_
 //   every CTA : wait for lp_done; turn shares into integer quotas; rewrite its slice.
 //
 // The ordinal ranges come from atomics, so which CTA gets which range differs from run
-// to run; quotas are exact regardless.  Shared memory: 5 int arrays of E entries.
+// to run; quotas are exact regardless.  Shared memory: 5 int arrays of E entries plus the
+// (D + 1) bundle sums per rank.
 template <int GP, int D, typename IdxT>
 __global__ void __launch_bounds__(kBlock) fused_run_kernel(const IdxT* __restrict__ idx, long long n, Topo tp,
                                                            Exchange ex, IpmParams prm, Workspace* ws,
@@ -516,7 +535,9 @@ __global__ void __launch_bounds__(kBlock) fused_run_kernel(const IdxT* __restric
     int* glob = ws_global(ws, e);
     for (int i = threadIdx.x; i < e; i += kBlock) glob[i] = summed[i];
     if (tracing) trace[3] = global_timer_ns();
-    solve_groups<GP, D>(summed, tp, 0, kWarps * (32 / GP), prm, probs, avail, status);
+    int* bundle = reinterpret_cast<int*>(phys + e);  // past the five E-sized tables
+    bundle_sums<D>(summed, tp, bundle, 0, tp.n_group * tp.g);
+    solve_groups<GP, D>(bundle, tp, 0, kWarps * (32 / GP), prm, probs, avail, status);
     __threadfence();
     __syncthreads();
     if (threadIdx.x == 0) st_release_gpu(&ws->lp_done, epoch);

@@ -44,6 +44,7 @@ cudaError_t dispatch_shape(int g, int d, Fn&& fn) {
 }
 
 size_t fused_smem(int e) { return sizeof(int) * 5 * (size_t)e; }
+size_t bundle_smem(const Topo& tp) { return sizeof(int) * (size_t)tp.n_group * tp.g * (tp.d + 1); }
 
 template <typename K>
 cudaError_t allow_smem(K kernel, size_t bytes) {
@@ -82,7 +83,10 @@ struct SolveLaunch {
   cudaError_t operator()() const {
     constexpr int per_cta = kWarps * (32 / GP);
     const int grid = (tp.n_group + per_cta - 1) / per_cta;
-    solve_kernel<GP, D><<<grid, kBlock, 0, stream>>>(workload, tp, prm, probs, normalised, avail, status);
+    const size_t smem = bundle_smem(tp);
+    cudaError_t err = allow_smem(solve_kernel<GP, D>, smem);
+    if (err != cudaSuccess) return err;
+    solve_kernel<GP, D><<<grid, kBlock, smem, stream>>>(workload, tp, prm, probs, normalised, avail, status);
     return cudaGetLastError();
   }
 };
@@ -144,7 +148,7 @@ struct FusedLaunch {
   template <int GP, int D>
   cudaError_t operator()() {
     auto kernel = fused_run_kernel<GP, D, IdxT>;
-    const size_t smem = fused_smem(tp.e);
+    const size_t smem = fused_smem(tp.e) + bundle_smem(tp);
     cudaError_t err = allow_smem(kernel, smem);
     if (err != cudaSuccess) return err;
     void* args[] = {&idx, &n, &tp, &ex, &prm, &ws, &probs, &avail, &status, &out, &grid_timeout_ns, &trace};
@@ -200,7 +204,8 @@ struct OccupancyQuery {
 
 int max_fused_ctas(int g, int d, int n_logical, int idx_is64) {
   int result = 0;
-  OccupancyQuery q{fused_smem(n_logical), idx_is64, &result};
+  // bundle sums add at most (d + 1) ints per rank: bounded by n_logical * (d + 1) / d
+  OccupancyQuery q{fused_smem(n_logical) + sizeof(int) * (size_t)n_logical * (d + 1), idx_is64, &result};
   if (dispatch_shape(g, d, q) != cudaSuccess) return 0;
   return result;
 }

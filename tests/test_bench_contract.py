@@ -1,0 +1,30 @@
+"""bench.py's reference arm must answer with one JSON line even where the reference cannot run."""
+
+import json
+import os
+import subprocess
+import sys
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_reference_arm_prints_one_json_line():
+    proc = subprocess.run(
+        [sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--steps", "3", "--warmup", "3"],
+        capture_output=True, text=True, timeout=600, cwd=ROOT,
+    )
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    lines = [ln for ln in proc.stdout.splitlines() if ln.startswith("{")]
+    assert len(lines) == 1
+    out = json.loads(lines[0])
+    assert out["impl"] == "reference"
+    assert "unavailable" in out or {"metric", "value", "unit", "n_gpus"} <= set(out)
+
+
+def test_bench_defaults_follow_the_contract():
+    sys.path.insert(0, ROOT)
+    import bench
+
+    args = bench.parse_args([])
+    assert args.gpus == 1 and args.warmup >= 3 and args.steps > 0 and args.impl == "ours"
+    assert bench.N_LOGICAL == 256 and bench.EP_SIZE == 8 and bench.TOKENS_PER_RANK == 4096 and bench.TOP_K == 8
