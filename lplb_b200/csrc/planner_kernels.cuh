@@ -195,11 +195,19 @@ __global__ void __launch_bounds__(kBlock) count_kernel(const IdxT* __restrict__ 
   __syncthreads();
   if (!last) return;
   __threadfence();
+  // Column-wise inclusive scan over the CTA rows.  Eight rows are loaded before any of them is
+  // stored back, so the loads of a batch overlap instead of queueing behind the stores.
   for (int i = threadIdx.x; i < e; i += kBlock) {
     int run = 0;
-    for (int r = 0; r < n_cta; ++r) {
-      run += __ldcg(&by_cta[(size_t)r * e + i]);
-      by_cta[(size_t)r * e + i] = run;
+    for (int r0 = 0; r0 < n_cta; r0 += 8) {
+      int v[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = r0 + j < n_cta ? __ldcg(&by_cta[(size_t)(r0 + j) * e + i]) : 0;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        run += v[j];
+        if (r0 + j < n_cta) by_cta[(size_t)(r0 + j) * e + i] = run;
+      }
     }
   }
   if (threadIdx.x == 0) ws->count_ticket = 0;
