@@ -163,7 +163,8 @@ def run_ours(args) -> dict:
     rank, world, local, group = dist_setup(args.gpus)
     dev = torch.device("cuda", local)
     planner = Planner(
-        cube(), N_LOGICAL + RED_PER_RANK * EP_SIZE, N_LOGICAL, EP_SIZE, group, device=dev, comm=args.comm
+        cube(), N_LOGICAL + RED_PER_RANK * EP_SIZE, N_LOGICAL, EP_SIZE, group, device=dev, comm=args.comm,
+        warm_start=not args.cold,
     )
     n_sms = args.n_sms or torch.cuda.get_device_properties(dev).multi_processor_count
     pl = planner.n_local_routed_experts
@@ -323,6 +324,7 @@ def run_ours(args) -> dict:
             "tokens_per_rank": TOKENS_PER_RANK,
             "parallelism": f"ep8-cube LP over {world} rank(s)",
             "comm": planner.comm,
+            "lp_warm_start": planner.warm_start,
             "n_sms": n_sms,
             "l2": "256 MiB buffer written between timed iterations",
             "slow_path": "update_redundancy_mapping runs at every bias redraw (50 steps), between timed chunks",
@@ -450,6 +452,7 @@ def parse_args(argv=None):
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--comm", choices=["auto", "p2p", "nccl", "none"], default="auto")
     ap.add_argument("--n-sms", type=int, default=0, help="CTAs used by the planner kernels (default: all SMs)")
+    ap.add_argument("--cold", action="store_true", help="solve every LP from scratch (Planner(warm_start=False))")
     ap.add_argument("--trace", action="store_true", help="add per-phase device times from the kernel's own stamps")
     ap.add_argument("--dump", default="", help="write the per-step device times (us) to this file")
     return ap.parse_args(argv)

@@ -91,6 +91,32 @@ class PlannerEngine {
     phy2log_ = to_dev_i32(phy2log);
     log2phy_ = to_dev_i32(log2phy);
     log2edge_ = to_dev_i32(log2edge);
+    invalidate_warm_start();  // a new placement is a new LP
+  }
+
+  // Warm starts: keep a centred iterate per group on the device and start the next solve from
+  // it while it still fits the data (see IpmParams in lp_solver.cuh).
+  void set_warm_start(bool on, double guard, double snap_mu) {
+    c10::cuda::CUDAGuard dev_guard(device_);
+    if (on) {
+      LPLB_CHECK(guard > 0 && snap_mu > 0, "guard and snap_mu must be positive");
+      if (!anchor_.defined()) {
+        auto f64 = torch::TensorOptions().dtype(torch::kFloat64).device(torch::kCUDA, device_);
+        anchor_ = torch::zeros({n_group_, g_, 4 * d_ + 3}, f64);
+        anchor_valid_ = torch::zeros({n_group_}, status_.options());
+      }
+      prm_.anchor = anchor_.data_ptr<double>();
+      prm_.anchor_valid = anchor_valid_.data_ptr<int>();
+      prm_.guard = guard;
+      prm_.snap_mu = snap_mu;
+    } else {
+      prm_.anchor = nullptr;
+      prm_.anchor_valid = nullptr;
+    }
+  }
+  // Forget the saved iterates (next solve of every group starts cold).  Stream-ordered.
+  void invalidate_warm_start() {
+    if (anchor_valid_.defined()) anchor_valid_.zero_();
   }
 
   void set_params(int max_iters, double tol, double peer_timeout_us, double grid_timeout_us) {
@@ -287,6 +313,7 @@ class PlannerEngine {
     c10::cuda::CUDAGuard guard(device_);
     LPLB_CUDA(cudaDeviceSynchronize());
     workspace_.zero_();
+    invalidate_warm_start();
     if (block_.base) LPLB_CUDA(cudaMemset(block_.base, 0, block_.bytes));
     LPLB_CUDA(cudaDeviceSynchronize());
   }
@@ -363,7 +390,7 @@ class PlannerEngine {
   lplb::SolveParams prm_{24, 1e-4};
   unsigned long long peer_timeout_ns_ = 1000000000ull, grid_timeout_ns_ = 1000000000ull;
   torch::Tensor r2o_, o2r_, phy2log_, log2phy_, log2edge_;
-  torch::Tensor workspace_, status_, probs_, trace_;
+  torch::Tensor workspace_, status_, probs_, trace_, anchor_, anchor_valid_;
   int max_cta64_ = -1, max_cta32_ = -1;
   // exchange
   IpcBlock block_;
@@ -386,6 +413,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def("set_topology", &PlannerEngine::set_topology)
       .def("set_mapping", &PlannerEngine::set_mapping)
       .def("set_params", &PlannerEngine::set_params)
+      .def("set_warm_start", &PlannerEngine::set_warm_start)
+      .def("invalidate_warm_start", &PlannerEngine::invalidate_warm_start)
       .def("count_idx", &PlannerEngine::count_idx)
       .def("solve", &PlannerEngine::solve)
       .def("map_idx", &PlannerEngine::map_idx)

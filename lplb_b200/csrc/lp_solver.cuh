@@ -36,6 +36,16 @@ namespace lplb {
 struct IpmParams {
   int max_iters;   // hard cap on iterations
   double tol;      // relative duality gap and feasibility target
+  // Warm start (optional).  `anchor` holds, per group and rank, a well-centred iterate
+  // (complementarity about `snap_mu`) saved by the last cold solve: f, v, z, q per bundle, then
+  // s, y, t.  A solve starts from it when the new data leave it nearly primal feasible (largest
+  // row residual <= `guard`, in units of the mean rank load), which is the case while
+  // consecutive batches come from the same distribution; otherwise it starts cold and
+  // replaces the anchor.  Null = always cold.
+  double* anchor = nullptr;  // [n_group][G][4 * D + 3]
+  int* anchor_valid = nullptr;  // [n_group]
+  double guard = 0.05;
+  double snap_mu = 1e-3;
 };
 
 struct IpmOutcome {
@@ -197,9 +207,12 @@ __device__ __forceinline__ double ldl8_solve(const Ldl8& m, int li, double g) {
 //   dst[d]    segment lane that holds the replica of own bundle d       (o2r[i][d])
 // Padding lanes (rank >= G) pass w = 0, fixed = 0, src = dst = li.
 // Returns the shares f[d] of own bundles kept on the origin, clamped to [0, 1].
+// `anchor` / `anchor_valid`: this lane's slot of the warm-start state and its group's flag
+// (both null when warm starts are off or the lane is padding).
 template <int GP, int D>
 __device__ IpmOutcome ipm_solve_segment(int li, const double (&w_in)[D], double fixed, const int (&src)[D],
-                                        const int (&dst)[D], const IpmParams prm, double (&f_out)[D]) {
+                                        const int (&dst)[D], const IpmParams prm, double (&f_out)[D],
+                                        double* anchor = nullptr, int* anchor_valid = nullptr) {
   constexpr double kEta = 0.995;
   constexpr int kComp = GP + 2 * GP * D;
 
@@ -251,6 +264,49 @@ __device__ IpmOutcome ipm_solve_segment(int li, const double (&w_in)[D], double 
     for (int d = 0; d < D; ++d) z[d] = q[d] = 2.0 * mu0;
   }
 
+  // ---- warm start from the anchor, if it still fits the data -----------------------------
+  // The decision is taken per segment; lanes without a slot (padding) follow their segment.
+  bool cold = true;
+  {
+    double fa[D], va[D], za[D], qa[D], sa = 1.0, ya = 1.0 / GP, ta = 0.0;
+    const bool have = anchor != nullptr && anchor_valid != nullptr && *anchor_valid != 0;
+#pragma unroll
+    for (int d = 0; d < D; ++d) {
+      fa[d] = have ? anchor[d] : 0.5;
+      va[d] = have ? anchor[D + d] : 0.5;
+      za[d] = have ? anchor[2 * D + d] : 1.0;
+      qa[d] = have ? anchor[3 * D + d] : 1.0;
+    }
+    if (have) {
+      sa = anchor[4 * D];
+      ya = anchor[4 * D + 1];
+      ta = anchor[4 * D + 2];
+    }
+    const double mfa = m_times(fa);  // shuffles inside: every lane takes part, with or without a slot
+    const double rp = have ? fabs(ta - base - mfa - sa) : 0.0;
+    // every reduction below is executed by all 32 lanes, whatever their segment decides
+    const bool seg_has = seg_max<GP>(have ? 1.0 : 0.0) > 0.0;
+    const double rp_max = seg_max<GP>(rp);
+    const double t_anchor = seg_max<GP>(have ? ta : -1e300);
+    const bool fits = seg_has && !empty && rp_max <= prm.guard;
+    if (fits && have) {
+#pragma unroll
+      for (int d = 0; d < D; ++d) {
+        f[d] = fa[d];
+        v[d] = va[d];
+        z[d] = za[d];
+        q[d] = qa[d];
+      }
+      s = sa;
+      y = ya;
+    }
+    if (fits) {
+      t = t_anchor;
+      cold = false;
+    }
+  }
+  bool saved = false;
+
   bool done = empty;
   int iters = 0;
   double gap = 1e300, gap_scale = 1.0;
@@ -279,6 +335,21 @@ __device__ IpmOutcome ipm_solve_segment(int li, const double (&w_in)[D], double 
       gap = primal - dual;  // absolute here, made relative once at the end
       gap_scale = fabs(primal);
       if (gap <= prm.tol * gap_scale && infeas <= prm.tol) done = true;
+    }
+    // A cold solve leaves its first iterate at or below snap_mu behind as the next anchor.
+    if (cold && !saved && !empty && anchor != nullptr && mu <= prm.snap_mu) {
+#pragma unroll
+      for (int d = 0; d < D; ++d) {
+        anchor[d] = f[d];
+        anchor[D + d] = v[d];
+        anchor[2 * D + d] = z[d];
+        anchor[3 * D + d] = q[d];
+      }
+      anchor[4 * D] = s;
+      anchor[4 * D + 1] = y;
+      anchor[4 * D + 2] = t;
+      if (li == 0 && anchor_valid != nullptr) *anchor_valid = 1;
+      saved = true;
     }
     // Every segment of the warp has to leave the loop together.
     if (__all_sync(0xffffffffu, done) || it == prm.max_iters) break;

@@ -34,6 +34,10 @@ struct ExchangeDesc {
 struct SolveParams {
   int max_iters;
   double tol;
+  double* anchor = nullptr;      // warm-start state [n_group][G][4 * D + 3], or null
+  int* anchor_valid = nullptr;   // [n_group]
+  double guard = 0.05;
+  double snap_mu = 1e-3;
 };
 
 // Largest group size / replicas per rank that the warp solver is instantiated for.

@@ -94,7 +94,7 @@ struct SolveLaunch {
 cudaError_t launch_solve(const int* workload, const TopoDesc& topo, SolveParams prm, float* probs, float* normalised,
                          void* avail, int avail_is64, int* status, cudaStream_t stream) {
   if (!shape_ok(topo)) return cudaErrorInvalidValue;
-  SolveLaunch l{workload, make_topo(topo), IpmParams{prm.max_iters, prm.tol}, probs, normalised,
+  SolveLaunch l{workload, make_topo(topo), IpmParams{prm.max_iters, prm.tol, prm.anchor, prm.anchor_valid, prm.guard, prm.snap_mu}, probs, normalised,
                 Counter{avail, avail_is64}, status, stream};
   return dispatch_shape(topo.g, topo.d, l);
 }
@@ -167,13 +167,13 @@ cudaError_t launch_fused(const void* idx, int idx_is64, long long n, const TopoD
   Exchange ex{exd.recv, exd.n_ranks, exd.my_rank, exd.timeout_ns};
   if (idx_is64) {
     FusedLaunch<int64_t> l{static_cast<const int64_t*>(idx), n, make_topo(topo), ex,
-                           IpmParams{prm.max_iters, prm.tol}, static_cast<Workspace*>(workspace), probs,
+                           IpmParams{prm.max_iters, prm.tol, prm.anchor, prm.anchor_valid, prm.guard, prm.snap_mu}, static_cast<Workspace*>(workspace), probs,
                            Counter{avail, avail_is64}, status, static_cast<int64_t*>(out), n_cta, grid_timeout_ns,
                            trace, cooperative, stream};
     return dispatch_shape(topo.g, topo.d, l);
   }
   FusedLaunch<int32_t> l{static_cast<const int32_t*>(idx), n, make_topo(topo), ex,
-                         IpmParams{prm.max_iters, prm.tol}, static_cast<Workspace*>(workspace), probs,
+                         IpmParams{prm.max_iters, prm.tol, prm.anchor, prm.anchor_valid, prm.guard, prm.snap_mu}, static_cast<Workspace*>(workspace), probs,
                          Counter{avail, avail_is64}, status, static_cast<int32_t*>(out), n_cta, grid_timeout_ns,
                          trace, cooperative, stream};
   return dispatch_shape(topo.g, topo.d, l);

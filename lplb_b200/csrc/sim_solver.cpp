@@ -7,7 +7,8 @@ namespace {
 
 template <int GP, int D>
 void solve_batch(int g, const int* r2o, const int* o2r, int nb, const double* w, const double* fixed, int max_iters,
-                 double tol, double* f_out, int* iters, int* converged) {
+                 double tol, double* f_out, int* iters, int* converged, double* anchor, int* anchor_valid,
+                 double guard, double snap_mu) {
   constexpr int kSeg = 32 / GP;
   for (int b0 = 0; b0 < nb; b0 += kSeg) {
     lplb_sim::run_warp([&](int lane) {
@@ -27,7 +28,10 @@ void solve_batch(int g, const int* r2o, const int* o2r, int nb, const double* w,
           dst[d] = o2r[li * D + d];
         }
       }
-      const lplb::IpmOutcome res = lplb::ipm_solve_segment<GP, D>(li, wl, fx, src, dst, lplb::IpmParams{max_iters, tol}, f);
+      lplb::IpmParams prm{max_iters, tol, anchor, anchor_valid, guard, snap_mu};
+      double* slot = live && anchor ? anchor + ((size_t)b * g + li) * (4 * D + 3) : nullptr;
+      int* flag = live && anchor ? anchor_valid + b : nullptr;
+      const lplb::IpmOutcome res = lplb::ipm_solve_segment<GP, D>(li, wl, fx, src, dst, prm, f, slot, flag);
       if (live) {
         for (int d = 0; d < D; ++d) f_out[((size_t)b * g + li) * D + d] = f[d];
         if (li == 0) {
@@ -41,16 +45,25 @@ void solve_batch(int g, const int* r2o, const int* o2r, int nb, const double* w,
 
 }  // namespace
 
-extern "C" int lplb_sim_solve(int g, int d, const int* r2o, const int* o2r, int nb, const double* w,
-                              const double* fixed, int max_iters, double tol, double* f_out, int* iters,
-                              int* converged) {
+// anchor [nb][g][4*d+3] and anchor_valid [nb] may be null (cold solves only).
+extern "C" int lplb_sim_solve_warm(int g, int d, const int* r2o, const int* o2r, int nb, const double* w,
+                                   const double* fixed, int max_iters, double tol, double* f_out, int* iters,
+                                   int* converged, double* anchor, int* anchor_valid, double guard, double snap_mu) {
   const int gp = g <= 8 ? 8 : (g <= 16 ? 16 : 32);
 #define LPLB_CASE(GP_, D_)                                                                             \
   if (gp == GP_ && d == D_) {                                                                          \
-    solve_batch<GP_, D_>(g, r2o, o2r, nb, w, fixed, max_iters, tol, f_out, iters, converged);          \
+    solve_batch<GP_, D_>(g, r2o, o2r, nb, w, fixed, max_iters, tol, f_out, iters, converged, anchor,   \
+                         anchor_valid, guard, snap_mu);                                                  \
     return 0;                                                                                          \
   }
   LPLB_CASE(8, 1) LPLB_CASE(8, 2) LPLB_CASE(8, 4) LPLB_CASE(16, 2) LPLB_CASE(32, 2) LPLB_CASE(32, 1)
 #undef LPLB_CASE
   return 1;
+}
+
+extern "C" int lplb_sim_solve(int g, int d, const int* r2o, const int* o2r, int nb, const double* w,
+                              const double* fixed, int max_iters, double tol, double* f_out, int* iters,
+                              int* converged) {
+  return lplb_sim_solve_warm(g, d, r2o, o2r, nb, w, fixed, max_iters, tol, f_out, iters, converged, nullptr, nullptr,
+                             0.05, 1e-3);
 }

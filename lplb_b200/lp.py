@@ -143,6 +143,8 @@ class IpmResult:
     gap: torch.Tensor  #: ``[B]`` final relative duality gap
     iters: torch.Tensor  #: ``[B]`` iterations used
     converged: torch.Tensor  #: ``[B]`` bool
+    anchor: dict | None = None  #: warm-start state to hand to the next call (see ``solve_ipm``)
+    warm: torch.Tensor | None = None  #: ``[B]`` bool, instances that started from the anchor
 
 
 def _chol_factor(n: torch.Tensor) -> torch.Tensor:
@@ -189,6 +191,10 @@ def solve_ipm(
     tol: float = 1e-4,
     dtype: torch.dtype = torch.float64,
     factor_dtype: torch.dtype | None = None,
+    anchor: dict | None = None,
+    warm_start: bool = False,
+    guard: float = 0.05,
+    snap_mu: float = 1e-3,
 ) -> IpmResult:
     """Batched primal-dual interior-point solve of the compact LP.
 
@@ -207,6 +213,15 @@ def solve_ipm(
     positive diagonal, factored once by Cholesky and reused for the predictor, the
     corrector and the border column that carries ``sum dy = r_t``.  Step lengths keep
     every positive quantity positive with a 0.995 fraction to the boundary.
+
+    Warm start (``warm_start=True``).  A cold solve saves its first iterate whose average
+    complementarity is at most ``snap_mu`` as the *anchor* (returned in ``result.anchor``;
+    pass it back in).  The next solve starts from the anchor when the new data leave it
+    nearly primal feasible, ``max_i |t - load_i(f) - s_i| <= guard`` in units of the mean
+    rank load, and cold otherwise (which refreshes the anchor).  Batches drawn from one
+    distribution keep fitting the same anchor and converge in one or two iterations; a shift
+    of the distribution trips the guard.  The residuals of the anchor are removed by the
+    Newton steps like any other infeasibility.
     """
     g, d = r2o.shape
     k = g * d
@@ -235,6 +250,30 @@ def solve_ipm(
     z = (mu0 / 0.5).expand(nb, k).clone()
     q = z.clone()
 
+    use_warm = torch.zeros(nb, dtype=torch.bool)
+    if warm_start and anchor is not None:
+        fa, va = anchor["f"].to(dtype), anchor["v"].to(dtype)
+        sa, ta = anchor["s"].to(dtype), anchor["t"].to(dtype)
+        rp = (ta.unsqueeze(1) - base - (m @ fa.unsqueeze(-1)).squeeze(-1) - sa).abs().max(1).values
+        use_warm = anchor["valid"].bool() & ~empty & (rp <= guard)
+        pick = use_warm.unsqueeze(1)
+        f, v = torch.where(pick, fa, f), torch.where(pick, va, v)
+        z, q = torch.where(pick, anchor["z"].to(dtype), z), torch.where(pick, anchor["q"].to(dtype), q)
+        s, y = torch.where(pick, sa, s), torch.where(pick, anchor["y"].to(dtype), y)
+        t = torch.where(use_warm, ta, t)
+    new_anchor = None
+    if warm_start:
+        if anchor is not None:
+            new_anchor = {key: val.clone() for key, val in anchor.items()}
+        else:
+            new_anchor = {
+                "f": torch.zeros(nb, k, dtype=dtype), "v": torch.zeros(nb, k, dtype=dtype),
+                "z": torch.zeros(nb, k, dtype=dtype), "q": torch.zeros(nb, k, dtype=dtype),
+                "s": torch.zeros(nb, g, dtype=dtype), "y": torch.zeros(nb, g, dtype=dtype),
+                "t": torch.zeros(nb, dtype=dtype), "valid": torch.zeros(nb, dtype=torch.bool),
+            }
+    saved = torch.zeros(nb, dtype=torch.bool)
+
     done = empty.clone()
     iters = torch.zeros(nb, dtype=torch.int64)
     gap = torch.where(empty, torch.zeros(nb, dtype=dtype), torch.full((nb,), float("inf"), dtype=dtype))
@@ -257,6 +296,13 @@ def solve_ipm(
         dual = (y * base).sum(1) - q.sum(1) + torch.minimum(r_d, torch.zeros_like(r_d)).sum(1)
         gap_now = (primal - dual) / primal.abs().clamp_min(1e-12)
         infeas = torch.maximum(r_u.abs().max(1).values, r_t.abs())
+        if new_anchor is not None:
+            take = ~use_warm & ~saved & ~empty & (mu <= snap_mu)
+            if bool(take.any()):
+                for key, val in (("f", f), ("v", v), ("z", z), ("q", q), ("s", s), ("y", y), ("t", t)):
+                    new_anchor[key][take] = val[take]
+                new_anchor["valid"][take] = True
+                saved = saved | take
         newly = (~done) & (gap_now <= tol) & (infeas <= tol)
         gap = torch.where(done, gap, gap_now)
         done = done | newly
@@ -317,6 +363,8 @@ def solve_ipm(
         gap=gap,
         iters=iters,
         converged=done,
+        anchor=new_anchor,
+        warm=use_warm,
     )
     return out
 

@@ -77,6 +77,9 @@ class Planner:
         peer_timeout_us: float = 1e6,
         grid_timeout_us: float = 1e6,
         allow_self_edges: bool = False,
+        warm_start: bool = False,
+        warm_guard: float = 0.05,
+        warm_snap_mu: float = 1e-3,
     ) -> None:
         """
         :param redundant_to_original: ``[group_size, num_redundants]``; rank ``i``'s
@@ -97,6 +100,13 @@ class Planner:
             group is on this host and falls back to ``nccl``.
         :param max_iters, tol: interior-point iteration cap and relative duality gap.
         :param peer_timeout_us, grid_timeout_us: budgets of the in-kernel waits.
+        :param warm_start: start every solve from a centred iterate saved by the last cold
+            solve of the same group, as long as the new statistics still fit it (largest row
+            residual at most ``warm_guard`` mean rank loads); typically one or two iterations
+            instead of three to five when consecutive batches come from one distribution.
+            Shares then depend on the planner's history, not only on the current batch; every
+            rank keeps its own (normally identical) state.  ``update_redundancy_mapping`` and
+            ``reset_exchange`` discard the state.
         """
         if device is None:
             device = "cuda" if torch.cuda.is_available() else "cpu"
@@ -138,6 +148,8 @@ class Planner:
         self.ep_group = group
         self.deep_ep_initialized = False  # name kept from the reference: "in-kernel exchange is live"
         self._n_sms_default: int | None = None
+        self.warm_start, self.warm_guard, self.warm_snap_mu = bool(warm_start), float(warm_guard), float(warm_snap_mu)
+        self._anchor: dict | None = None  # CPU path only; the engine keeps its own on the device
         self._host_out: tuple | None = None
 
         self._engine = None
@@ -155,6 +167,7 @@ class Planner:
             )
             self._engine.set_topology(self.r2o, self.o2r)
             self._engine.set_params(self.max_iters, self.tol, float(peer_timeout_us), float(grid_timeout_us))
+            self._engine.set_warm_start(bool(warm_start), float(warm_guard), float(warm_snap_mu))
 
         self.mapping: ExpertMapping
         self.phy2log: torch.Tensor
@@ -201,6 +214,12 @@ class Planner:
         """
         self.init_peer_exchange()
 
+    def invalidate_warm_start(self) -> None:
+        """Forget the saved iterates; the next solve of every group starts cold."""
+        self._anchor = None
+        if self._engine is not None:
+            self._engine.invalidate_warm_start()
+
     def reset_exchange(self) -> None:
         """Collective: re-zero epochs, flags and buffers on every rank (e.g. after a timeout)."""
         if self._engine is None:
@@ -230,6 +249,7 @@ class Planner:
             n_nodes=self.n_nodes,
         )
         assert mapping.phy2log.numel() == self.n_routed_experts
+        self._anchor = None  # a new placement is a new LP
         self.mapping = mapping.to(self.device)
         self.phy2log = self.mapping.phy2log
         if self._engine is not None:
@@ -289,7 +309,11 @@ class Planner:
             self.n_local_logical_routed_experts,
             self.combined_redundant_experts,
         )
-        res = _lp.solve_ipm(w, fixed, self.r2o.cpu(), max_iters=self.max_iters, tol=self.tol)
+        res = _lp.solve_ipm(
+            w, fixed, self.r2o.cpu(), max_iters=self.max_iters, tol=self.tol, warm_start=self.warm_start,
+            anchor=self._anchor, guard=self.warm_guard, snap_mu=self.warm_snap_mu,
+        )
+        self._anchor = res.anchor
         avail_counter += int(res.converged.sum())
         peak = wl.max().clamp_min(1).float()
         return res.f.float().to(self.device), (wl.float() / peak).view(shape)

@@ -98,6 +98,24 @@ def main():
     probs_s, _ = staged.solve_probs(local_counts, avail)
     assert torch.equal(probs_s, planner.last_probs)
 
+    # 4b. warm-started solves stay identical on every rank (same history, same arithmetic)
+    warm = Planner(cube(), 256 + 16, 256, 8, group, device=dev, comm="p2p", warm_start=True)
+    warm.load_state_dict(planner.state_dict())
+    warm_iters = []
+    for step in range(6):
+        logits = torch.randn(4096, 256, device=dev, generator=gen) + bias
+        idx = logits.bfloat16().topk(8, dim=-1).indices
+        avail.zero_()
+        warm.run(idx, avail)
+        probs = warm.last_probs.clone()
+        gathered = [torch.empty_like(probs) for _ in range(world)]
+        dist.all_gather(gathered, probs, group=group)
+        assert all(torch.equal(g, probs) for g in gathered), "warm-started shares differ between ranks"
+        st = warm.check_status(clear=True)
+        assert st.ok and int(avail) == 1
+        warm_iters.append(st["lp_iters"])
+    assert min(warm_iters[1:]) < warm_iters[0], warm_iters
+
     # 5. expert-parallel MoE layer over the same ranks: dispatch and combine cross NVLink
     from lplb_b200 import ring
     from lplb_b200.models.moe import MoELayer

@@ -278,6 +278,48 @@ def test_run_reads_and_writes_pinned_host_memory():
     assert planner.check_status().ok
 
 
+def test_warm_start_cuts_iterations_and_keeps_the_optimum():
+    planner = _planner(topology.cube(), 256, 8, 2, warm_start=True)
+    cold = _planner(topology.cube(), 256, 8, 2)
+    gen = torch.Generator("cuda").manual_seed(9)
+    bias = torch.randn(256, device="cuda", generator=gen)
+
+    def batch():
+        return (torch.randn(8192, 256, device="cuda", generator=gen) + bias).bfloat16().topk(8, dim=-1).indices
+
+    hist = torch.bincount(batch().reshape(-1), minlength=256)
+    planner.update_redundancy_mapping(hist)
+    cold.update_redundancy_mapping(hist)
+    avail = torch.zeros(1, dtype=torch.int32, device="cuda")
+    iters = []
+    for step in range(8):
+        if step == 5:
+            bias = torch.randn(256, device="cuda", generator=gen)  # the routing distribution moves
+        idx = batch()
+        out = planner.run(idx, avail)
+        _check_redirect(planner, idx, out, planner.last_probs)
+        st = planner.check_status(clear=True)
+        assert st.ok
+        cold.run(idx, avail)
+        iters.append((st["lp_iters"], cold.check_status(clear=True)["lp_iters"]))
+        counts = torch.bincount(idx.reshape(-1), minlength=256)
+        w, fixed = lp.bundle_loads(counts.cpu().double(), planner.phy2log.cpu(), 1, 8, 2, 32, 1)
+        realised = float(lp.rank_loads(planner.last_probs.cpu().double(), w, fixed, topology.cube()).max())
+        _, t_opt = lp.solve_highs(w[0], fixed[0], topology.cube())
+        assert (realised - t_opt) / t_opt < 1e-3
+        # the staged kernels share the state: same anchor, same answer
+        local, _ = planner.count_workload(idx, _sms())
+        staged_probs, _ = planner.solve_probs(local, avail)
+        assert torch.allclose(staged_probs, planner.last_probs, atol=1e-6)
+    assert iters[0][0] == iters[0][1]  # first solve is cold
+    assert all(w <= c for w, c in iters)
+    assert iters[2][0] < iters[2][1] and iters[3][0] < iters[3][1]  # steady state: fewer iterations
+    assert iters[5][0] == iters[5][1]  # the guard sent the shifted batch down the cold path
+    planner.invalidate_warm_start()
+    planner.run(batch(), avail)
+    assert planner.check_status()["lp_iters"] >= iters[0][0] - 1
+
+
 # ---------------------------------------------------------------- exchange on one GPU
 def test_exchange_loopback_sums_prefilled_peer():
     planner = _planner(topology.cube(), 64, 8, 2)

@@ -117,3 +117,29 @@ def test_planner_solve_quality_cpu(name, r2o, n_logical, ep_size, n_red, reorder
     for grp in range(planner.n_group):
         _, t_opt = lp.solve_highs(w[grp], fixed[grp], r2o)
         assert (float(realised[grp]) - t_opt) / t_opt < 1e-3
+
+
+def test_warm_start_is_optional_and_safe():
+    r2o = topology.torus(2, 4)
+    gen = torch.Generator().manual_seed(4)
+    mean = (torch.rand(2, 8, 8, generator=gen, dtype=torch.float64) + 0.5) * 1000
+    anchor, iters = None, []
+    for step in range(6):
+        cnt = (mean * (1 + 0.03 * torch.randn(2, 8, 8, generator=gen, dtype=torch.float64))).floor()
+        if step == 4:
+            cnt[1] = 0  # an empty group neither uses nor writes the anchor
+        w, fixed = cnt[:, :, :2].contiguous(), cnt[:, :, 2:].sum(-1)
+        res = lp.solve_ipm(w, fixed, r2o, warm_start=True, anchor=anchor)
+        anchor = res.anchor
+        cold = lp.solve_ipm(w, fixed, r2o)
+        assert cold.anchor is None and bool(res.converged.all())
+        for b in range(2):
+            if float(w[b].sum() + fixed[b].sum()) == 0:
+                continue
+            _, t_opt = lp.solve_highs(w[b], fixed[b], r2o)
+            assert (float(res.t[b]) - t_opt) / t_opt < 1e-3
+        iters.append((res.iters.tolist(), cold.iters.tolist(), res.warm.tolist()))
+    assert iters[0][2] == [False, False] and iters[1][2] == [True, True]
+    assert iters[4][2] == [True, False] and iters[5][2] == [True, True]
+    assert all(w_it <= c_it for its in iters for w_it, c_it in zip(its[0], its[1]))
+    assert sum(iters[2][0]) < sum(iters[2][1])

@@ -82,3 +82,40 @@ def test_iteration_cap_is_reported(sim):
     f, iters, conv = _solve(sim, r2o, w, fixed, max_iters=1, tol=1e-9)
     assert not conv.any() and iters.tolist() == [1, 1]
     assert bool(((f >= 0) & (f <= 1)).all())
+
+
+def test_warm_start_on_device_code_matches_the_torch_restatement(sim):
+    """A stream of similar batches, then a shifted one: the anchor logic of the device code
+    (run under warp emulation) takes the same decisions and iterations as lp.solve_ipm."""
+    r2o = topology.cube()
+    g, d = r2o.shape
+    gen = torch.Generator().manual_seed(11)
+    mean = (torch.rand(g, 8, generator=gen, dtype=torch.float64) + 0.5) * 4096
+    anchor_c = np.zeros((1, g, 4 * d + 3))
+    valid_c = np.zeros(1, np.int32)
+    anchor_t = None
+    r = np.ascontiguousarray(r2o.numpy().astype(np.int32))
+    o = np.ascontiguousarray(topology.invert_r2o(r2o).numpy().astype(np.int32))
+    ptr = lambda a: ctypes.c_void_p(a.ctypes.data)  # noqa: E731
+    seen = []
+    for step in range(5):
+        if step == 3:
+            mean = mean.flip(0) * torch.linspace(0.3, 2.0, 8, dtype=torch.float64)  # the distribution moves
+        cnt = (mean * (1 + 0.02 * torch.randn(g, 8, generator=gen, dtype=torch.float64))).floor().unsqueeze(0)
+        w, fixed = cnt[:, :, :d].contiguous(), cnt[:, :, d:].sum(-1)
+        ref = lp.solve_ipm(w, fixed, r2o, tol=1e-4, warm_start=True, anchor=anchor_t)
+        anchor_t = ref.anchor
+        wa, fa = np.ascontiguousarray(w.numpy()), np.ascontiguousarray(fixed.numpy())
+        f = np.zeros((1, g, d))
+        iters, conv = np.zeros(1, np.int32), np.zeros(1, np.int32)
+        rc = sim.lplb_sim_solve_warm(g, d, ptr(r), ptr(o), 1, ptr(wa), ptr(fa), 24, ctypes.c_double(1e-4), ptr(f),
+                                     ptr(iters), ptr(conv), ptr(anchor_c), ptr(valid_c), ctypes.c_double(0.05),
+                                     ctypes.c_double(1e-3))
+        assert rc == 0 and conv[0] == 1
+        assert int(iters[0]) == int(ref.iters[0])
+        assert float((torch.from_numpy(f) - ref.f).abs().max()) < 1e-5
+        _, t_opt = lp.solve_highs(w[0], fixed[0], r2o)
+        assert (float(lp.rank_loads(torch.from_numpy(f[0]), w[0], fixed[0], r2o).max()) - t_opt) / t_opt < 1e-3
+        seen.append((bool(ref.warm[0]), int(iters[0])))
+    assert [s[0] for s in seen] == [False, True, True, False, True]  # cold, warm, warm, guard trips, warm
+    assert seen[1][1] < seen[0][1] and seen[2][1] < seen[0][1]
