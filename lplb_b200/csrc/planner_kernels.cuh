@@ -498,6 +498,12 @@ __global__ void __launch_bounds__(kBlock) fused_run_kernel(const IdxT* __restric
       asm volatile("prefetch.global.L2 [%0];" ::"l"(tp.r2o));
       asm volatile("prefetch.global.L2 [%0];" ::"l"(tp.o2r));
     }
+    if (prm.anchor != nullptr) {  // warm-start state: (4 D + 3) doubles per rank
+      const int n_bytes = tp.n_group * tp.g * (4 * D + 3) * 8;
+      for (int b = threadIdx.x * 128; b < n_bytes; b += kBlock * 128)
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const char*>(prm.anchor) + b));
+      if (threadIdx.x == 1) asm volatile("prefetch.global.L2 [%0];" ::"l"(prm.anchor_valid));
+    }
     histogram_keep(idx, begin, end, e, hist, status, keep);
   } else {
     histogram_keep(idx, begin, end, e, hist, status, keep);
