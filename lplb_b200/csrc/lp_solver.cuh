@@ -487,4 +487,16 @@ __device__ IpmOutcome ipm_solve_segment(int li, const double (&w_in)[D], double 
   return out;
 }
 
+// Out-of-line entry for the 32-rank instantiation.  Inlined into a kernel, the 32-register-pair
+// matrix row plus the caller's own state no longer fit the register file and the compiler
+// moves the row to local memory, which costs an order of magnitude; as a separate function
+// the solver gets the whole register budget to itself.
+template <int GP, int D>
+__device__ __noinline__ IpmOutcome ipm_solve_segment_ool(int li, const double (&w_in)[D], double fixed,
+                                                         const int (&src)[D], const int (&dst)[D],
+                                                         const IpmParams prm, double (&f_out)[D], double* anchor,
+                                                         int* anchor_valid) {
+  return ipm_solve_segment<GP, D>(li, w_in, fixed, src, dst, prm, f_out, anchor, anchor_valid);
+}
+
 }  // namespace lplb

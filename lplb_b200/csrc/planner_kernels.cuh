@@ -281,7 +281,9 @@ __device__ void solve_groups(const int* __restrict__ bundle, const Topo& tp, int
       anchor = prm.anchor + ((size_t)grp * tp.g + li) * (4 * D + 3);
       anchor_valid = prm.anchor_valid + grp;
     }
-    const IpmOutcome res = ipm_solve_segment<GP, D>(li, w, fixed, src, dst, prm, f, anchor, anchor_valid);
+    IpmOutcome res;
+    if constexpr (GP == 32) res = ipm_solve_segment_ool<GP, D>(li, w, fixed, src, dst, prm, f, anchor, anchor_valid);
+    else res = ipm_solve_segment<GP, D>(li, w, fixed, src, dst, prm, f, anchor, anchor_valid);
     if (live) {
 #pragma unroll
       for (int d = 0; d < D; ++d) probs[((size_t)grp * tp.g + li) * D + d] = (float)f[d];
