@@ -4,7 +4,7 @@ redirect): EP8 Cube, 256 + 16 experts, 4096 tokens x top-8, a handful of launche
 
     python benchmarks/profile_planner_stages.py
     ncu --set full --clock-control none -k regex:"count_kernel|solve_kernel|redirect_kernel" -s 9 -c 3 \
-        -o gpurun_out/planner_stages python benchmarks/profile_planner_stages.py
+        -o planner_stages python benchmarks/profile_planner_stages.py
 """
 
 import os
