@@ -334,7 +334,8 @@ __device__ IpmOutcome ipm_solve_segment(int li, const double (&w_in)[D], double 
     if (!done) {
       gap = primal - dual;  // absolute here, made relative once at the end
       gap_scale = fabs(primal);
-      if (gap <= prm.tol * gap_scale && infeas <= prm.tol) done = true;
+      // at mu ~ 1e-13 the iterate is optimal to machine precision: stop instead of dividing by it
+      if ((gap <= prm.tol * gap_scale && infeas <= prm.tol) || mu <= 1e-13) done = true;
     }
     // A cold solve leaves its first iterate at or below snap_mu behind as the next anchor.
     if (cold && !saved && !empty && anchor != nullptr && mu <= prm.snap_mu) {

@@ -273,6 +273,11 @@ def solve_ipm(
                 "t": torch.zeros(nb, dtype=dtype), "valid": torch.zeros(nb, dtype=torch.bool),
             }
     saved = torch.zeros(nb, dtype=torch.bool)
+    # the feasible iterate with the smallest gap seen so far: what is returned if the loop
+    # ends without meeting `tol` (a tolerance below what float arithmetic can certify)
+    best_gap = torch.full((nb,), float("inf"), dtype=dtype)
+    best_f = f.clone()
+    stopped = torch.zeros(nb, dtype=torch.bool)
 
     done = empty.clone()
     iters = torch.zeros(nb, dtype=torch.int64)
@@ -303,7 +308,11 @@ def solve_ipm(
                     new_anchor[key][take] = val[take]
                 new_anchor["valid"][take] = True
                 saved = saved | take
-        newly = (~done) & (gap_now <= tol) & (infeas <= tol)
+        # at mu ~ 1e-13 the iterate is optimal to machine precision: stop instead of dividing by it
+        better = (~done) & (gap_now < best_gap) & (infeas <= max(tol, 1e-9))
+        best_gap = torch.where(better, gap_now, best_gap)
+        best_f = torch.where(better.unsqueeze(1), f, best_f)
+        newly = (~done) & (((gap_now <= tol) & (infeas <= tol)) | (mu <= 1e-13))
         gap = torch.where(done, gap, gap_now)
         done = done | newly
         if bool(done.all()):
@@ -345,16 +354,25 @@ def solve_ipm(
         df, dv, dt, ds, dy, dz, dq = newton(sm - s * y - ds * dy, sm - z * f - dz * df, sm - q * v - dq * dv)
         ap = (eta * torch.minimum(torch.minimum(max_step(s, ds), max_step(f, df)), max_step(v, dv))).clamp_max(1.0)
         ad = (eta * torch.minimum(torch.minimum(max_step(y, dy), max_step(z, dz)), max_step(q, dq))).clamp_max(1.0)
-        live = (~done).to(dtype)
-        ap, ad = ap * live, ad * live
-        f = f + ap[:, None] * df
-        v = v + ap[:, None] * dv
-        t = t + ap * dt
-        s = s + ap[:, None] * ds
-        y = y + ad[:, None] * dy
-        z = z + ad[:, None] * dz
-        q = q + ad[:, None] * dq
+        # A step that is not finite (an instance pushed far past convergence by a tolerance
+        # tighter than the arithmetic allows) is not taken: that instance stops where it is.
+        cand = (f + ap[:, None] * df, v + ap[:, None] * dv, t + ap * dt, s + ap[:, None] * ds,
+                y + ad[:, None] * dy, z + ad[:, None] * dz, q + ad[:, None] * dq)
+        finite = torch.ones(nb, dtype=torch.bool)
+        for c in cand:
+            finite &= torch.isfinite(c.reshape(nb, -1)).all(1)
+        stopped = stopped | (~done & ~finite)
+        done = done | ~finite
+        move = (~done) & finite
 
+        def upd(old, new):
+            return torch.where(move.view(-1, *([1] * (old.dim() - 1))), new, old)
+
+        f, v, t, s, y, z, q = (upd(o, c) for o, c in zip((f, v, t, s, y, z, q), cand))
+
+    certified = done & ~stopped
+    f = torch.where(certified.unsqueeze(1), f, best_f)
+    gap = torch.where(certified, gap, best_gap)
     f = torch.where(empty.unsqueeze(1), torch.ones_like(f), f.clamp(0.0, 1.0))
     load = base + (m @ f.unsqueeze(-1)).squeeze(-1)
     out = IpmResult(
@@ -362,7 +380,7 @@ def solve_ipm(
         t=load.max(1).values * scale,
         gap=gap,
         iters=iters,
-        converged=done,
+        converged=certified,
         anchor=new_anchor,
         warm=use_warm,
     )
