@@ -56,7 +56,8 @@ def main():
     red = r2o.shape[1]
     n_logical = args.experts_per_rank * world
     sizes = [int(s) for s in args.sizes.split(",")]
-    planner = Planner(r2o, n_logical + red * world, n_logical, world, group, device=dev, comm="p2p", n_nodes=2)
+    planner = Planner(r2o, n_logical + red * world, n_logical, world, group, device=dev, comm="p2p", n_nodes=2,
+                      exchange_node_size=world // 2 if world >= 4 else 0)  # two "nodes": two-level exchange
     layer = MoELayer(planner, args.hidden, args.inter, args.topk, max(sizes), group=group, capacity_factor=3.0)
     pl = planner.n_local_routed_experts
 

@@ -217,7 +217,7 @@ class PlannerEngine {
       LPLB_CHECK(!host_idx, "pass a pinned `out` tensor together with pinned host indices");
       out = torch::empty_like(idx);
     }
-    lplb::ExchangeDesc ex{nullptr, 1, 0, peer_timeout_ns_};
+    lplb::ExchangeDesc ex{nullptr, 1, 0, 0, peer_timeout_ns_};
     if (use_exchange) {
       LPLB_CHECK(exchange_open_, "exchange buffers are not open; call open_exchange first");
       ex = exchange_desc();
@@ -291,13 +291,14 @@ class PlannerEngine {
 
   // Test hook: make it look as if `rank` had published `counts` for launch number `epoch`
   // (the launch after `completed_launches()` has epoch completed + 1).
-  void debug_fill_slot(int rank, const torch::Tensor& counts, int64_t epoch) {
+  void debug_fill_slot(int rank, const torch::Tensor& counts, int64_t epoch, int level) {
     LPLB_CHECK(block_.base && rank >= 0 && rank < n_ranks_, "no exchange block or bad rank");
     LPLB_CHECK(counts.numel() == e_, "counts must have E entries");
     c10::cuda::CUDAGuard guard(device_);
     auto words = (counts.to(torch::kCPU, torch::kInt64).contiguous() & 0xffffffffLL) + (epoch << 32);
     LPLB_CUDA(cudaDeviceSynchronize());
-    auto* slot = static_cast<unsigned long long*>(block_.base) + ((size_t)(epoch & 1) * n_ranks_ + rank) * e_;
+    LPLB_CHECK(level == 0 || level == 1, "level is 0 or 1");
+    auto* slot = static_cast<unsigned long long*>(block_.base) + (((size_t)(epoch & 1) * 2 + level) * n_ranks_ + rank) * e_;
     LPLB_CUDA(cudaMemcpy(slot, words.data_ptr<int64_t>(), sizeof(int64_t) * e_, cudaMemcpyHostToDevice));
   }
 
@@ -328,6 +329,13 @@ class PlannerEngine {
     cudaFree(block_.base);
     block_.base = nullptr;
     exchange_open_ = false;
+  }
+
+  // Two-level schedule of the exchange: ranks form nodes of `node_size` consecutive ranks
+  // (must divide the rank count); 0 restores the one-level all-to-all.
+  void set_exchange_nodes(int node_size) {
+    LPLB_CHECK(node_size >= 0 && (node_size == 0 || (n_ranks_ % node_size == 0)), "node_size must divide the rank count");
+    node_size_ = node_size;
   }
 
   // Cooperative launch (default) makes the driver guarantee that all CTAs of the fused kernel
@@ -362,7 +370,7 @@ class PlannerEngine {
 
   lplb::ExchangeDesc exchange_desc() const {
     return lplb::ExchangeDesc{reinterpret_cast<unsigned long long* const*>(recv_table_.data_ptr()), n_ranks_,
-                              my_rank_, peer_timeout_ns_};
+                              my_rank_, node_size_, peer_timeout_ns_};
   }
 
   void require_mapping() const {
@@ -396,7 +404,7 @@ class PlannerEngine {
   IpcBlock block_;
   std::vector<void*> peers_;
   torch::Tensor recv_table_;
-  int n_ranks_ = 1, my_rank_ = 0;
+  int n_ranks_ = 1, my_rank_ = 0, node_size_ = 0;
   bool exchange_open_ = false;
   bool cooperative_ = true;
 };
@@ -424,12 +432,14 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def("alloc_exchange", &PlannerEngine::alloc_exchange)
       .def("open_exchange", &PlannerEngine::open_exchange)
       .def("open_exchange_loopback", &PlannerEngine::open_exchange_loopback)
-      .def("debug_fill_slot", &PlannerEngine::debug_fill_slot)
+      .def("debug_fill_slot", &PlannerEngine::debug_fill_slot, py::arg("rank"), py::arg("counts"), py::arg("epoch"),
+           py::arg("level") = 0)
       .def("completed_launches", &PlannerEngine::completed_launches)
       .def("reset_exchange", &PlannerEngine::reset_exchange)
       .def("close_exchange", &PlannerEngine::close_exchange)
       .def("exchange_open", &PlannerEngine::exchange_open)
       .def("set_cooperative", &PlannerEngine::set_cooperative)
+      .def("set_exchange_nodes", &PlannerEngine::set_exchange_nodes)
       .def("enable_trace", &PlannerEngine::enable_trace)
       .def("trace", &PlannerEngine::trace)
       .def("status", &PlannerEngine::status)

@@ -25,9 +25,10 @@ struct TopoDesc {
 
 struct ExchangeDesc {
   unsigned long long* const* recv;  // device array of n_ranks pointers (nullptr when n_ranks == 1);
-                                    // each points at that rank's uint64[2][n_ranks][E] receive buffer
+                                    // each points at that rank's uint64[2][2][n_ranks][E] receive buffer
   int n_ranks;
   int my_rank;
+  int node_size;                    // two-level schedule over nodes of this many ranks; 0 = one level
   unsigned long long timeout_ns;
 };
 
@@ -46,7 +47,7 @@ constexpr int kMaxDup = 4;
 constexpr int kMaxLogicalExperts = 8192;
 
 size_t planner_workspace_bytes(int n_logical);
-inline size_t exchange_buffer_bytes(int n_ranks, int n_logical) { return sizeof(unsigned long long) * 2 * (size_t)n_ranks * n_logical; }
+inline size_t exchange_buffer_bytes(int n_ranks, int n_logical) { return sizeof(unsigned long long) * 4 * (size_t)n_ranks * n_logical; }
 
 // idx_is64: 1 for int64 indices, 0 for int32.  All functions return a cudaError_t from the
 // launch (cudaSuccess when enqueued); cudaErrorInvalidValue for unsupported shapes.

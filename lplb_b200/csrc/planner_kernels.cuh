@@ -27,11 +27,12 @@ struct Topo {
 };
 
 // Peer-memory exchange state.  recv[r] points at rank r's receive buffer
-// uint64[2][n_ranks][E] (two epochs' worth); every word is (epoch << 32) | count.
+// uint64[2 parities][2 levels][n_ranks][E]; every word is (epoch << 32) | count.
 struct Exchange {
   unsigned long long* const* recv;
   int n_ranks;
   int my_rank;
+  int node_size;  // ranks per node for the two-level schedule; 0 or n_ranks = one level
   unsigned long long timeout_ns;
 };
 
@@ -376,23 +377,27 @@ __device__ __forceinline__ void st_volatile_u64(unsigned long long* p, unsigned 
   asm volatile("st.volatile.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
 }
 
-__device__ __forceinline__ unsigned exchange_counts(const Exchange& ex, uint32_t epoch, int e, const int* mine,
-                                                    int* sum) {
-  __shared__ unsigned missing;
+// One level of the exchange among the peers first_peer, first_peer + stride, ... (n_peers of
+// them, this rank included): push `mine` into slot [parity][level][my_rank] of each, wait for
+// their words in this rank's buffer, sum.  Adds the ranks that never arrived to `missing`.
+__device__ __forceinline__ void exchange_level(const Exchange& ex, uint32_t epoch, int e, int level, int first_peer,
+                                               int stride, int n_peers, const int* mine, int* sum,
+                                               unsigned* missing) {
   const int parity = epoch & 1;
-  if (threadIdx.x == 0) missing = 0;
-  __syncthreads();
+  const size_t level_base = ((size_t)parity * 2 + level) * ex.n_ranks;
   const unsigned long long tag = (unsigned long long)epoch << 32;
-  for (int r = 0; r < ex.n_ranks; ++r) {
-    unsigned long long* slot = ex.recv[r] + ((size_t)parity * ex.n_ranks + ex.my_rank) * e;
+  for (int j = 0; j < n_peers; ++j) {
+    const int r = first_peer + j * stride;
+    unsigned long long* slot = ex.recv[r] + (level_base + ex.my_rank) * e;
     for (int i = threadIdx.x; i < e; i += kBlock) st_volatile_u64(&slot[i], tag | (uint32_t)mine[i]);
   }
-  const unsigned long long* base = ex.recv[ex.my_rank] + (size_t)parity * ex.n_ranks * e;
+  const unsigned long long* base = ex.recv[ex.my_rank] + level_base * e;
   // pass 1: wait until every word of this thread's elements carries the epoch
   unsigned late = 0;
   const uint64_t t0 = global_timer_ns();
   for (int i = threadIdx.x; i < e; i += kBlock) {
-    for (int r = 0; r < ex.n_ranks; ++r) {
+    for (int j = 0; j < n_peers; ++j) {
+      const int r = first_peer + j * stride;
       if ((late >> (r & 31)) & 1u) continue;
       const unsigned long long* word = &base[(size_t)r * e + i];
       uint32_t spins = 0;
@@ -407,20 +412,43 @@ __device__ __forceinline__ unsigned exchange_counts(const Exchange& ex, uint32_t
       }
     }
   }
-  if (late) atomicOr(&missing, late);
+  if (late) atomicOr(missing, late);
   __syncthreads();
-  const unsigned miss = missing;
-  // pass 2: sum; an absent peer contributes this rank's own counts instead of stale data
+  const unsigned miss = *missing;
+  // pass 2: sum; an absent peer contributes this rank's own vector instead of stale data
   for (int i = threadIdx.x; i < e; i += kBlock) {
     int acc = 0;
-    for (int r = 0; r < ex.n_ranks; ++r) {
+    for (int j = 0; j < n_peers; ++j) {
+      const int r = first_peer + j * stride;
       const bool absent = (miss >> (r & 31)) & 1u;
       acc += absent ? mine[i] : (int)(uint32_t)ld_volatile_u64(&base[(size_t)r * e + i]);
     }
     sum[i] = acc;
   }
   __syncthreads();
-  return miss;
+}
+
+// All-reduce over all ranks.  With ex.node_size < n_ranks it runs in two levels, the schedule
+// of a machine whose ranks form nodes of node_size (the reference reduces inside a node over
+// NVLink and between nodes over the network, reference minilp.cu:111-163): first among the
+// ranks of this rank's node, then the node sums among the ranks with the same position in
+// every node; (node_size - 1) + (n_nodes - 1) partners instead of n_ranks - 1.  `mine` is
+// overwritten with the node sum in that case.
+__device__ __forceinline__ unsigned exchange_counts(const Exchange& ex, uint32_t epoch, int e, int* mine, int* sum) {
+  __shared__ unsigned missing;
+  if (threadIdx.x == 0) missing = 0;
+  __syncthreads();
+  const int s = ex.node_size;
+  if (s <= 0 || s >= ex.n_ranks) {
+    exchange_level(ex, epoch, e, 0, 0, 1, ex.n_ranks, mine, sum, &missing);
+  } else {
+    const int node = ex.my_rank / s, local = ex.my_rank - node * s;
+    exchange_level(ex, epoch, e, 0, node * s, 1, s, mine, sum, &missing);
+    for (int i = threadIdx.x; i < e; i += kBlock) mine[i] = sum[i];
+    __syncthreads();
+    exchange_level(ex, epoch, e, 1, local, s, ex.n_ranks / s, mine, sum, &missing);
+  }
+  return missing;
 }
 
 // ---------------------------------------------------------------------------------------

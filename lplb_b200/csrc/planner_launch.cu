@@ -120,7 +120,7 @@ cudaError_t launch_redirect(const void* idx, int idx_is64, long long n, const fl
 cudaError_t launch_exchange(const int* in, int n_logical, const ExchangeDesc& exd, void* workspace, int* out,
                             int* status, cudaStream_t stream) {
   if (n_logical < 1 || n_logical > kMaxLogicalExperts || exd.n_ranks < 2) return cudaErrorInvalidValue;
-  Exchange ex{exd.recv, exd.n_ranks, exd.my_rank, exd.timeout_ns};
+  Exchange ex{exd.recv, exd.n_ranks, exd.my_rank, exd.node_size, exd.timeout_ns};
   const size_t smem = sizeof(int) * 2 * (size_t)n_logical;
   cudaError_t err = allow_smem(exchange_kernel, smem);
   if (err != cudaSuccess) return err;
@@ -164,7 +164,7 @@ cudaError_t launch_fused(const void* idx, int idx_is64, long long n, const TopoD
                          void* out, int n_cta, unsigned long long grid_timeout_ns, unsigned long long* trace,
                          int cooperative, cudaStream_t stream) {
   if (!shape_ok(topo) || n_cta < 1) return cudaErrorInvalidValue;
-  Exchange ex{exd.recv, exd.n_ranks, exd.my_rank, exd.timeout_ns};
+  Exchange ex{exd.recv, exd.n_ranks, exd.my_rank, exd.node_size, exd.timeout_ns};
   if (idx_is64) {
     FusedLaunch<int64_t> l{static_cast<const int64_t*>(idx), n, make_topo(topo), ex,
                            IpmParams{prm.max_iters, prm.tol, prm.anchor, prm.anchor_valid, prm.guard, prm.snap_mu}, static_cast<Workspace*>(workspace), probs,

@@ -80,6 +80,7 @@ class Planner:
         warm_start: bool = False,
         warm_guard: float = 0.05,
         warm_snap_mu: float = 1e-3,
+        exchange_node_size: int = 0,
     ) -> None:
         """
         :param redundant_to_original: ``[group_size, num_redundants]``; rank ``i``'s
@@ -107,6 +108,9 @@ class Planner:
             Shares then depend on the planner's history, not only on the current batch; every
             rank keeps its own (normally identical) state.  ``update_redundancy_mapping`` and
             ``reset_exchange`` discard the state.
+        :param exchange_node_size: run the in-kernel statistics exchange in two levels, inside
+            nodes of this many consecutive ranks and then between nodes (the schedule for a
+            topology that spans nodes, e.g. ``torus(2, 4)`` with 4); 0 = one all-to-all level.
         """
         if device is None:
             device = "cuda" if torch.cuda.is_available() else "cpu"
@@ -150,6 +154,7 @@ class Planner:
         self._n_sms_default: int | None = None
         self.warm_start, self.warm_guard, self.warm_snap_mu = bool(warm_start), float(warm_guard), float(warm_snap_mu)
         self._anchor: dict | None = None  # CPU path only; the engine keeps its own on the device
+        self.exchange_node_size = int(exchange_node_size)
         self._host_out: tuple | None = None
 
         self._engine = None
@@ -202,6 +207,10 @@ class Planner:
         if self._engine is None or self.ep_group is None:
             raise RuntimeError("peer exchange needs a CUDA device and a process group")
         open_peer_exchange(self._engine, self.ep_group, self.device)
+        if self.exchange_node_size:
+            if self.ep_group.size() % self.exchange_node_size:
+                raise ValueError("exchange_node_size must divide the number of ranks")
+            self._engine.set_exchange_nodes(self.exchange_node_size)
         self.deep_ep_initialized = True
         self.comm = "p2p"
 

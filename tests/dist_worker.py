@@ -98,6 +98,22 @@ def main():
     probs_s, _ = staged.solve_probs(local_counts, avail)
     assert torch.equal(probs_s, planner.last_probs)
 
+    # 4a. two-level schedule (nodes of world/2 ranks) is bitwise equal to the all-reduce as well
+    if world >= 4:
+        two = Planner(cube(), 256 + 16, 256, 8, group, device=dev, comm="p2p", exchange_node_size=world // 2)
+        for step in range(10):
+            mine = torch.randint(0, 5000, (256,), device=dev, generator=gen, dtype=torch.int32)
+            want = mine.clone()
+            dist.all_reduce(want, group=group)
+            assert torch.equal(two._engine.all_reduce_counts(mine), want), f"rank {rank}: two-level exchange differs"
+        idx = (torch.randn(2048, 256, device=dev, generator=gen) + bias).topk(8, dim=-1).indices
+        counts = torch.bincount(idx.reshape(-1), minlength=256)
+        dist.all_reduce(counts, group=group)
+        avail.zero_()
+        two.run(idx, avail)
+        assert torch.equal(two._engine.workspace()[8 + 2 * 256 : 8 + 3 * 256].long(), counts)
+        assert two.check_status().ok
+
     # 4b. warm-started solves stay identical on every rank (same history, same arithmetic)
     warm = Planner(cube(), 256 + 16, 256, 8, group, device=dev, comm="p2p", warm_start=True)
     warm.load_state_dict(planner.state_dict())

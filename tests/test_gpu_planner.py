@@ -343,6 +343,35 @@ def test_exchange_loopback_sums_prefilled_peer():
     _check_redirect(planner, idx, out, eng.last_probs())
 
 
+def test_two_level_exchange_on_one_gpu():
+    # 4 ranks in 2 nodes of 2, this GPU plays rank 0: level 0 needs rank 1 (same node), level 1
+    # needs the node sum published by rank 2 (same position in the other node)
+    planner = _planner(topology.cube(), 64, 8, 2)
+    eng = planner._engine
+    eng.open_exchange_loopback(4, 0)
+    eng.set_exchange_nodes(2)
+    neighbour = torch.arange(64, dtype=torch.int32) + 1
+    other_node = torch.arange(64, dtype=torch.int32) * 5 + 2
+    mine = torch.randint(0, 100, (64,), dtype=torch.int32, device="cuda")
+    for _ in range(3):
+        epoch = eng.completed_launches() + 1
+        eng.debug_fill_slot(1, neighbour, epoch, 0)
+        eng.debug_fill_slot(2, other_node, epoch, 1)
+        got = eng.all_reduce_counts(mine)
+        assert torch.equal(got.cpu(), mine.cpu() + neighbour + other_node)
+    # the other node never answers: reported, its share replaced by this node's sum
+    planner2 = _planner(topology.cube(), 64, 8, 2, peer_timeout_us=300.0)
+    eng2 = planner2._engine
+    eng2.open_exchange_loopback(4, 0)
+    eng2.set_exchange_nodes(2)
+    eng2.debug_fill_slot(1, neighbour, 1, 0)
+    got = eng2.all_reduce_counts(mine)
+    torch.cuda.synchronize()
+    assert torch.equal(got.cpu(), 2 * (mine.cpu() + neighbour))
+    st = planner2.check_status(clear=True)
+    assert st["error"] == "peer_timeout" and st["detail"] == 0b100
+
+
 def test_exchange_wait_runs_out_and_falls_back():
     # a flag that nothing sets: the wait must end by itself, report, and still route
     planner = _planner(topology.cube(), 64, 8, 2, peer_timeout_us=300.0)
