@@ -56,8 +56,9 @@ class PlannerEngine {
  public:
   PlannerEngine(int n_group, int g, int d, int ll, int c, int device)
       : n_group_(n_group), g_(g), d_(d), ll_(ll), c_(c), device_(device) {
-    LPLB_CHECK(g >= 1 && g <= lplb::kMaxGroupSize, "group size must be 1.." << lplb::kMaxGroupSize << ", got " << g);
-    LPLB_CHECK(d >= 1 && d <= lplb::kMaxDup, "replicas per rank must be 1.." << lplb::kMaxDup << ", got " << d);
+    // Groups beyond the warp solver's sizes can still be counted and redirected here; their LP
+    // is solved by the caller (see Planner.solve_probs).
+    LPLB_CHECK(g >= 1 && d >= 1, "group size and replicas per rank must be positive");
     LPLB_CHECK(ll >= c * d, "local logical experts < replicated experts");
     e_ = n_group * g * ll;
     LPLB_CHECK(e_ <= lplb::kMaxLogicalExperts, "too many logical experts: " << e_);
@@ -144,6 +145,7 @@ class PlannerEngine {
     LPLB_CHECK(workload.is_cuda() && workload.scalar_type() == torch::kInt32 && workload.is_contiguous(),
                "workload must be a contiguous int32 CUDA tensor");
     LPLB_CHECK(workload.numel() == e_, "workload must have " << e_ << " entries, got " << workload.numel());
+    LPLB_CHECK(has_native_solver(), "no warp solver for this group size; use the tensor-op solver");
     check_avail(avail);
     c10::cuda::CUDAGuard guard(device_);
     auto probs = torch::empty({n_group_, g_, d_}, probs_.options());
@@ -202,6 +204,8 @@ class PlannerEngine {
     check_avail(avail);
     c10::cuda::CUDAGuard guard(device_);
     const int is64 = idx.scalar_type() == torch::kInt64;
+    LPLB_CHECK(has_native_solver(), "the fused kernel needs a group of at most " << lplb::kMaxGroupSize
+                                        << " ranks with at most " << lplb::kMaxDup << " replicas each");
     int& limit = is64 ? max_cta64_ : max_cta32_;
     if (limit < 0) limit = lplb::max_fused_ctas(g_, d_, e_, is64);
     LPLB_CHECK(limit > 0, "fused kernel cannot be resident on this device");
@@ -356,6 +360,7 @@ class PlannerEngine {
   torch::Tensor last_probs() const { return probs_; }
   torch::Tensor workspace() const { return workspace_; }
   int n_logical() const { return e_; }
+  bool has_native_solver() const { return g_ <= lplb::kMaxGroupSize && d_ <= lplb::kMaxDup; }
   int max_fused_ctas(bool is64) {
     c10::cuda::CUDAGuard guard(device_);
     return lplb::max_fused_ctas(g_, d_, e_, is64);
@@ -446,6 +451,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def("last_probs", &PlannerEngine::last_probs)
       .def("workspace", &PlannerEngine::workspace)
       .def("n_logical", &PlannerEngine::n_logical)
+      .def("has_native_solver", &PlannerEngine::has_native_solver)
       .def("max_fused_ctas", &PlannerEngine::max_fused_ctas);
   bind_moe(m);
   m.attr("MAX_GROUP_SIZE") = lplb::kMaxGroupSize;

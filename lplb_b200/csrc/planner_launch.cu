@@ -25,9 +25,12 @@ Topo make_topo(const TopoDesc& t) {
 
 int padded_group(int g) { return g <= 8 ? 8 : (g <= 16 ? 16 : 32); }
 
-bool shape_ok(const TopoDesc& t) {
-  return t.g >= 1 && t.g <= kMaxGroupSize && t.d >= 1 && t.d <= kMaxDup && t.n_group >= 1 && t.ll >= t.c * t.d &&
-         (long long)t.n_group * t.g * t.ll <= kMaxLogicalExperts;
+// The counting and redirect kernels work for any topology; the warp solver (and with it the
+// fused kernel) is instantiated for groups of up to kMaxGroupSize ranks and kMaxDup replicas.
+bool shape_ok(const TopoDesc& t, bool need_solver = true) {
+  const bool tables = t.g >= 1 && t.d >= 1 && t.n_group >= 1 && t.ll >= t.c * t.d &&
+                      (long long)t.n_group * t.g * t.ll <= kMaxLogicalExperts;
+  return tables && (!need_solver || (t.g <= kMaxGroupSize && t.d <= kMaxDup));
 }
 
 // Calls fn.template operator()<GP, D>() for the instantiation that covers (g, d).
@@ -101,7 +104,7 @@ cudaError_t launch_solve(const int* workload, const TopoDesc& topo, SolveParams 
 
 cudaError_t launch_redirect(const void* idx, int idx_is64, long long n, const float* probs, const int* by_cta,
                             const TopoDesc& topo, int n_cta, void* out, cudaStream_t stream) {
-  if (!shape_ok(topo) || n_cta < 1) return cudaErrorInvalidValue;
+  if (!shape_ok(topo, false) || n_cta < 1) return cudaErrorInvalidValue;
   const Topo tp = make_topo(topo);
   const size_t smem = fused_smem(tp.e);
   cudaError_t err;

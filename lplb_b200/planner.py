@@ -158,6 +158,7 @@ class Planner:
         self._host_out: tuple | None = None
 
         self._engine = None
+        self._native_solver = False
         if self.device.type == "cuda":
             from . import _native
 
@@ -170,6 +171,12 @@ class Planner:
                 self.combined_redundant_experts,
                 self.device.index,
             )
+            self._native_solver = bool(self._engine.has_native_solver())
+            if not self._native_solver:
+                log.warning(
+                    "group of %d ranks x %d replicas exceeds the warp solver; the LP runs as tensor ops (slow path)",
+                    self.group_size, self.num_redundants,
+                )
             self._engine.set_topology(self.r2o, self.o2r)
             self._engine.set_params(self.max_iters, self.tol, float(peer_timeout_us), float(grid_timeout_us))
             self._engine.set_warm_start(bool(warm_start), float(warm_guard), float(warm_snap_mu))
@@ -302,8 +309,19 @@ class Planner:
             elif self.comm == "nccl":
                 wl = wl.clone()
                 torch.distributed.all_reduce(wl, group=self.ep_group)
-            probs, normalised = self._engine.solve(wl, avail_counter)
-            return probs, normalised.view(shape)
+            if self._native_solver:
+                probs, normalised = self._engine.solve(wl, avail_counter)
+                return probs, normalised.view(shape)
+            # groups larger than the warp solver's 32 ranks (or more than 4 replicas per rank):
+            # the same interior-point method as batched tensor ops on the device
+            w, fixed = _lp.bundle_loads(
+                wl.double(), self.phy2log, self.n_group, self.group_size, self.num_redundants,
+                self.n_local_logical_routed_experts, self.combined_redundant_experts,
+            )
+            res = _lp.solve_ipm(w.cpu(), fixed.cpu(), self.r2o.cpu(), max_iters=self.max_iters, tol=self.tol)
+            avail_counter += int(res.converged.sum())
+            peak = wl.max().clamp_min(1).float()
+            return res.f.float().to(self.device), (wl.float() / peak).view(shape)
 
         wl = workload.reshape(-1).to(torch.int64)
         if self.comm == "nccl":
@@ -364,7 +382,7 @@ class Planner:
         if n_sms is None:
             n_sms = self._default_sms()
         with self._nvtx("lplb_b200.planner.run"):
-            if self._engine is not None and self.comm in ("p2p", "none"):
+            if self._engine is not None and self.comm in ("p2p", "none") and self._native_solver:
                 if not idx.is_cuda and out is None:
                     key = (tuple(idx.shape), idx.dtype)
                     if self._host_out is None or self._host_out[0] != key:

@@ -343,6 +343,26 @@ def test_exchange_loopback_sums_prefilled_peer():
     _check_redirect(planner, idx, out, eng.last_probs())
 
 
+def test_groups_beyond_the_warp_solver_take_the_tensor_op_path():
+    # torus(8, 8): one LP group of 64 ranks.  Counting and redirect stay native, the LP runs as
+    # batched tensor ops; the public API is unchanged.
+    planner = _planner(topology.torus(8, 8), 512, 64, 2)
+    assert planner._native_solver is False
+    gen = torch.Generator("cuda").manual_seed(2)
+    idx = (torch.randn(4096, 512, device="cuda", generator=gen) + torch.randn(512, device="cuda", generator=gen)).topk(8, dim=-1).indices
+    planner.update_redundancy_mapping(torch.bincount(idx.reshape(-1), minlength=512))
+    avail = torch.zeros(1, dtype=torch.int32, device="cuda")
+    counts, by_sm = planner.count_workload(idx, _sms())
+    probs, _ = planner.solve_probs(counts, avail)
+    assert int(avail) == 1 and probs.shape == (1, 64, 2)
+    out = planner.run(idx, avail)
+    _check_redirect(planner, idx, out, probs)
+    w, fixed = lp.bundle_loads(counts.cpu().double(), planner.phy2log.cpu(), 1, 64, 2, 8, 1)
+    realised = float(lp.rank_loads(probs.cpu().double(), w, fixed, topology.torus(8, 8)).max())
+    _, t_opt = lp.solve_highs(w[0], fixed[0], topology.torus(8, 8))
+    assert (realised - t_opt) / t_opt < 1e-3
+
+
 def test_two_level_exchange_on_one_gpu():
     # 4 ranks in 2 nodes of 2, this GPU plays rank 0: level 0 needs rank 1 (same node), level 1
     # needs the node sum published by rank 2 (same position in the other node)
