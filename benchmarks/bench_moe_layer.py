@@ -44,6 +44,7 @@ def main():
     ap.add_argument("--skew", type=float, default=1.0)
     ap.add_argument("--capacity-factor", type=float, default=3.0)
     ap.add_argument("--fuse-dispatch", action="store_true", help="send rows from inside the first GEMM kernel")
+    ap.add_argument("--send-ctas", type=int, default=0, help="with --fuse-dispatch: CTAs that only send rows")
     ap.add_argument("--json", default="")
     args = ap.parse_args()
 
@@ -62,6 +63,7 @@ def main():
     layer = MoELayer(planner, args.hidden, args.inter, args.topk, args.tokens, group=group,
                      capacity_factor=args.capacity_factor)
     layer.fuse_dispatch = args.fuse_dispatch
+    layer.send_ctas = args.send_ctas
     pl = planner.n_local_routed_experts
 
     total = args.warmup + args.steps
@@ -128,6 +130,7 @@ def main():
         out = {
             "n_gpus": world,
             "fuse_dispatch": args.fuse_dispatch,
+            "send_ctas": args.send_ctas,
             "topology": "cube" if world == 8 else f"ring{world}",
             "shape": {"hidden": args.hidden, "inter": args.inter, "experts": n_logical + red * world,
                       "topk": args.topk, "tokens_per_rank": args.tokens, "skew": args.skew},

@@ -35,6 +35,7 @@ def main():
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--skew", type=float, default=0.0, help="std of the per-expert logit bias")
     ap.add_argument("--fuse-dispatch", action="store_true")
+    ap.add_argument("--send-ctas", type=int, default=0, help="with --fuse-dispatch: CTAs that only send rows")
     ap.add_argument("--json", default="")
     args = ap.parse_args()
     dev = torch.device("cuda", 0)
@@ -51,6 +52,7 @@ def main():
         w13[s] = interleave_gate_up(gate, up)
         w2[s] = (torch.randn(h, i, device=dev, generator=g) * i**-0.5).bfloat16()
     eng.set_weights(w13, w2)
+    eng.set_send_ctas(args.send_ctas)
     x = torch.randn(t, h, device=dev, generator=g).bfloat16()
     logits = torch.randn(t, e, device=dev, generator=g) + args.skew * torch.randn(e, device=dev, generator=g)
     wts, idx = torch.softmax(logits, -1).topk(k, dim=-1)

@@ -73,11 +73,13 @@ cudaError_t launch_dispatch(const LayerShape& sh, const LayerBuffers& b, const v
 // Step 2a (fused path only): decide the send order and every pair's target row and return slot.
 cudaError_t launch_schedule(const LayerShape& sh, const LayerBuffers& b, const void* phys_idx, int idx_is64,
                             int n_tokens, int n_cta, cudaStream_t stream);
-// Step 2b+3 fused: the first grouped GEMM with four extra warps per CTA that stream this rank's
-// rows to their targets while the tensor cores work on the experts whose rows have landed.
+// Step 2b+3 fused: the first grouped GEMM, which also streams this rank's rows to their targets
+// while the tensor cores work on the experts whose rows have landed.  send_ctas == 0: four
+// extra warps in every CTA send.  send_ctas > 0: that many of the n_cta CTAs only send and the
+// other n_cta - send_ctas only run tiles.
 cudaError_t launch_dispatch_gemm(const LayerShape& sh, const LayerBuffers& b, const CUtensorMap& tmap_a,
                                  const CUtensorMap& tmap_b, const void* x, uint32_t epoch,
-                                 unsigned long long timeout_ns, int n_cta, cudaStream_t stream);
+                                 unsigned long long timeout_ns, int n_cta, int send_ctas, cudaStream_t stream);
 // Step 3/4: grouped GEMMs.  which = 0: recv_x x w13 -> SwiGLU -> act.  which = 1: act x w2 -> peers' comb.
 cudaError_t launch_gemm(const LayerShape& sh, const LayerBuffers& b, const CUtensorMap& tmap_a,
                         const CUtensorMap& tmap_b, int which, uint32_t epoch, unsigned long long timeout_ns,

@@ -194,7 +194,7 @@ class MoeEngine {
     if (fused) {
       MOE_CUDA(lplb::moe::launch_schedule(sh_, buf_, phys_idx.data_ptr(), is64, n_tokens, n_cta, s));
       MOE_CUDA(lplb::moe::launch_dispatch_gemm(sh_, buf_, tm_x_, tm_w13_, x.data_ptr(), epoch_, timeout_ns_,
-                                               gemm_ctas(), s));
+                                               gemm_ctas(), send_ctas_, s));
     } else {
       MOE_CUDA(lplb::moe::launch_dispatch(sh_, buf_, x.data_ptr(), phys_idx.data_ptr(), is64, n_tokens, n_cta,
                                           epoch_, s));
@@ -210,6 +210,12 @@ class MoeEngine {
   }
 
   void set_timeout_us(double us) { timeout_ns_ = (unsigned long long)(us * 1e3); }
+  // Fused dispatch: 0 = four sender warps beside the tile roles in every CTA; n > 0 = n CTAs
+  // (of one per SM) only send rows and the rest only run tiles.
+  void set_send_ctas(int n) {
+    MOE_CHECK(n >= 0 && n < gemm_ctas(), "send_ctas must be in [0, number of GEMM CTAs)");
+    send_ctas_ = n;
+  }
   torch::Tensor status() const { return status_; }
   torch::Tensor plan() const { return plan_; }
   torch::Tensor act() const { return act_; }
@@ -285,6 +291,7 @@ class MoeEngine {
   bool ready_ = false, have_weights_ = false;
   uint32_t epoch_ = 0;
   unsigned long long timeout_ns_ = 2000000000ull;
+  int send_ctas_ = 0;
 };
 
 }  // namespace
@@ -302,6 +309,7 @@ void bind_moe(py::module_& m) {
       .def("forward", &MoeEngine::forward, py::arg("x"), py::arg("phys_idx"), py::arg("weights"), py::arg("n_cta"),
            py::arg("upto") = 5, py::arg("fuse_dispatch") = false)
       .def("set_timeout_us", &MoeEngine::set_timeout_us)
+      .def("set_send_ctas", &MoeEngine::set_send_ctas)
       .def("status", &MoeEngine::status)
       .def("plan", &MoeEngine::plan)
       .def("act", &MoeEngine::act)

@@ -72,8 +72,10 @@ struct GemmArgs {
   unsigned* ticket;       // zero before launch; left at zero
   int* status;            // first error code
   unsigned long long timeout_ns;
-  // fused dispatch (FUSED kernels only): this rank's rows are sent by warps 6-9 while the
-  // tensor cores work; an expert's tiles start once `arrived[e]` reached `arrive_target[e]`.
+  // fused dispatch (FUSED kernels only): this rank's rows are sent while the tensor cores
+  // work; an expert's tiles start once `arrived[e]` reached `arrive_target[e]`.  With
+  // send_ctas == 0 warps 6-9 of every CTA send; with send_ctas > 0 the last `send_ctas`
+  // CTAs of the grid do nothing but send (all their warps) and the others only run tiles.
   const __nv_bfloat16* x;        // [tokens, hidden] local hidden states
   const int* send_pair;          // [n_send] (local expert << 20) | pair index, in send order
   const int* send_target;        // [n_send] (rank << 24) | row, or -1
@@ -84,16 +86,33 @@ struct GemmArgs {
   int* recv_meta[kMaxRanks];
   uint32_t* arrived[kMaxRanks];  // per rank: [n_experts] cumulative rows landed
   int topk, hidden;
+  int send_ctas;
   unsigned long long* debug;     // optional [gridDim.x * 4] ns: kernel start, senders done, producer wait, end
 };
 
-constexpr int kSendWarps = 4;
-constexpr int kFusedThreads = kGemmThreads + 32 * kSendWarps;
+constexpr int kSendWarps = 4;        // sender warps per CTA when every CTA also runs tiles
+constexpr int kFusedThreads = 512;   // a dedicated sender CTA uses all 16 warps
+constexpr int kFusedWarps = kFusedThreads / 32;
+
+// One warp copies a row of `n_vec` 16-byte words with U independent loads in flight per lane.
+template <int U>
+__device__ __forceinline__ void copy_row(const uint4* __restrict__ src, uint4* __restrict__ dst, int n_vec, int lane) {
+  int v = lane;
+  for (; v + 32 * (U - 1) < n_vec; v += 32 * U) {
+    uint4 q[U];
+#pragma unroll
+    for (int i = 0; i < U; ++i) q[i] = __ldg(&src[v + 32 * i]);
+#pragma unroll
+    for (int i = 0; i < U; ++i) dst[v + 32 * i] = q[i];
+  }
+  for (; v < n_vec; v += 32) dst[v] = __ldg(&src[v]);
+}
 
 // Sender role of the fused kernel: warp `gw` of `n_gw` streams blocks of eight consecutive
 // send positions.  After a block, every lane fences its stores at system scope, the warp
 // re-converges, and one lane per row bumps the target expert's arrival counter on the
 // receiving GPU, which is what the receiver's TMA producer polls.
+template <int U>
 __device__ __forceinline__ void send_rows(const GemmArgs& a, int gw, int n_gw, int lane) {
   const int n_send = *a.n_send;
   const int vec_per_row = a.hidden / 8;
@@ -110,15 +129,7 @@ __device__ __forceinline__ void send_rows(const GemmArgs& a, int gw, int n_gw, i
       const int pair = pr & 0xFFFFF, dr = tg >> 24, row = tg & 0xFFFFFF;
       const uint4* src = reinterpret_cast<const uint4*>(a.x + (size_t)(pair / a.topk) * a.hidden);
       uint4* dst = reinterpret_cast<uint4*>(a.recv_x[dr] + (size_t)row * a.hidden);
-      int v = lane;
-      for (; v + 96 < vec_per_row; v += 128) {  // four independent 16-byte loads in flight per lane
-        const uint4 q0 = __ldg(&src[v]), q1 = __ldg(&src[v + 32]), q2 = __ldg(&src[v + 64]), q3 = __ldg(&src[v + 96]);
-        dst[v] = q0;
-        dst[v + 32] = q1;
-        dst[v + 64] = q2;
-        dst[v + 96] = q3;
-      }
-      for (; v < vec_per_row; v += 32) dst[v] = __ldg(&src[v]);
+      copy_row<U>(src, dst, vec_per_row, lane);
       if (lane == 0) a.recv_meta[dr][row] = (a.my_rank << 20) | a.pair_slot[pair];
     }
     __threadfence_system();
@@ -176,6 +187,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   __shared__ int s_flags_ok;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // CTAs [0, n_gemm) run tiles; in the fused kernel the rest (if any) only send rows
+  const int n_gemm = FUSED ? (int)gridDim.x - args.send_ctas : (int)gridDim.x;
+  const bool sender_cta = FUSED && (int)blockIdx.x >= n_gemm;
   unsigned long long* dbg = FUSED && args.debug ? args.debug + 4 * blockIdx.x : nullptr;
 
   if (threadIdx.x == 0) {
@@ -220,13 +234,17 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   const uint64_t budget = args.timeout_ns;
   const bool go = s_flags_ok != 0;
 
-  if (go && warp == 0) {
+  if (sender_cta) {
+    // ---------------- dedicated sender CTA (never waits on anything) ----------------
+    send_rows<7>(args, ((int)blockIdx.x - n_gemm) * kFusedWarps + warp, args.send_ctas * kFusedWarps, lane);
+    if (dbg && lane == 0) atomicMax(&dbg[1], (unsigned long long)timer_ns());
+  } else if (go && warp == 0) {
     // ---------------- TMA producer ----------------
     if (elect_one()) {
       TileCursor cur;
       uint32_t it = 0;  // running k-block counter over all tiles of this CTA
       int ready_expert = -1;
-      for (int t = blockIdx.x; cur.seek(t, args) && !*abort; t += gridDim.x) {
+      for (int t = blockIdx.x; cur.seek(t, args) && !*abort; t += n_gemm) {
         if (FUSED && cur.expert != ready_expert) {
           // all rows of this expert must have landed (senders on every GPU count them in)
           const uint32_t* ctr = args.arrived[args.my_rank] + cur.expert;
@@ -268,7 +286,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       constexpr uint32_t idesc = umma_idesc_bf16(kBM, kBN);
       TileCursor cur;
       uint32_t it = 0, tile_n = 0;
-      for (int t = blockIdx.x; cur.seek(t, args) && !*abort; t += gridDim.x, ++tile_n) {
+      for (int t = blockIdx.x; cur.seek(t, args) && !*abort; t += n_gemm, ++tile_n) {
         const uint32_t acc = tile_n & 1, acc_ph = (tile_n >> 1) & 1;
         if (!mbar_wait(bar_tempty + 8 * acc, acc_ph ^ 1, abort, budget)) break;
         tc_fence_after_sync();
@@ -297,15 +315,17 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       }
     }
   } else if (FUSED && warp >= 6) {
-    // ---------------- senders (never wait on anything) ----------------
-    send_rows(args, blockIdx.x * kSendWarps + (warp - 6), gridDim.x * kSendWarps, lane);
-    if (dbg && lane == 0) atomicMax(&dbg[1], (unsigned long long)timer_ns());
+    // ---------------- sender warps beside the tile roles (never wait on anything) ----------------
+    if (args.send_ctas == 0 && warp < 6 + kSendWarps) {
+      send_rows<4>(args, blockIdx.x * kSendWarps + (warp - 6), gridDim.x * kSendWarps, lane);
+      if (dbg && lane == 0) atomicMax(&dbg[1], (unsigned long long)timer_ns());
+    }
   } else if (go && warp >= 2) {
     // ---------------- epilogue ----------------
     const int quarter = warp & 3;  // TMEM lanes 32*quarter .. +31 are the ones this warp may read
     TileCursor cur;
     uint32_t tile_n = 0;
-    for (int t = blockIdx.x; cur.seek(t, args) && !*abort; t += gridDim.x, ++tile_n) {
+    for (int t = blockIdx.x; cur.seek(t, args) && !*abort; t += n_gemm, ++tile_n) {
       const uint32_t acc = tile_n & 1, acc_ph = (tile_n >> 1) & 1;
       const int local = t - cur.first_tile;
       const int m = local % cur.tiles_m, n = local / cur.tiles_m;

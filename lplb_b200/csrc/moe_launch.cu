@@ -133,11 +133,12 @@ cudaError_t launch_schedule(const LayerShape& sh, const LayerBuffers& b, const v
 
 cudaError_t launch_dispatch_gemm(const LayerShape& sh, const LayerBuffers& b, const CUtensorMap& tmap_a,
                                  const CUtensorMap& tmap_b, const void* x, uint32_t epoch,
-                                 unsigned long long timeout_ns, int n_cta, cudaStream_t stream) {
-  if (!shape_ok(sh) || n_cta < 1) return cudaErrorInvalidValue;
+                                 unsigned long long timeout_ns, int n_cta, int send_ctas, cudaStream_t stream) {
+  if (!shape_ok(sh) || n_cta < 1 || send_ctas < 0 || send_ctas >= n_cta) return cudaErrorInvalidValue;
   const int P = sh.n_ranks * sh.n_local;
   int* tail = plan_tail(sh, b);
   GemmArgs a{};
+  a.send_ctas = send_ctas;
   a.rows = b.plan;
   a.row_start = b.plan + sh.n_local;
   a.n_experts = sh.n_local;

@@ -94,6 +94,7 @@ class MoELayer:
         if group is not None:
             dist.barrier(group=group)
         self.fuse_dispatch = False
+        self.send_ctas = 0  # fused dispatch only: this many CTAs send rows and run no tiles (0: sender warps in every CTA)
         self._placed_for: torch.Tensor | None = None
         self.place_weights()
 
@@ -147,6 +148,8 @@ class MoELayer:
             raise RuntimeError("expert placement changed: call place_weights() first")
         n_cta = torch.cuda.get_device_properties(self.device).multi_processor_count
         fuse = self.fuse_dispatch if fuse_dispatch is None else fuse_dispatch
+        if fuse:
+            self.engine.set_send_ctas(int(self.send_ctas))
         return self.engine.forward(x.contiguous(), phys_idx.contiguous(), weights.float().contiguous(), n_cta, upto, fuse)
 
     def forward(self, x, logical_idx, weights, avail_counter, policy: str = "lplb"):

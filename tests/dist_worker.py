@@ -157,6 +157,7 @@ def main():
             layer.place_weights()
         avail.zero_()
         layer.fuse_dispatch = step >= 2  # later steps send the rows from inside the first GEMM
+        layer.send_ctas = 16 if step >= 3 else 0  # and the last ones from CTAs that run no tiles
         out = layer.forward(x, idx, w, avail, "lplb" if step % 2 == 0 else "static")
         torch.cuda.synchronize(dev)
         assert layer.check() == 0, layer.engine.status().tolist()

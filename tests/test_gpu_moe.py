@@ -76,14 +76,17 @@ def test_layer_matches_fp32_reference(hidden, inter, tokens, topk):
     layer.place_weights()
     avail = torch.zeros(1, dtype=torch.int32, device="cuda")
     ref = layer.reference_forward(x, idx, w).float()
-    for policy, fuse in (("lplb", False), ("static", False), ("lplb", True), ("static", True), ("lplb", False)):
-        layer.fuse_dispatch = fuse  # True: rows are sent from inside the first GEMM kernel
+    # fuse: 0 = stand-alone dispatch, 1 = rows sent by extra warps of the first GEMM kernel,
+    # 2 = rows sent by 16 CTAs of that kernel that run no tiles
+    for policy, fuse in (("lplb", 0), ("static", 0), ("lplb", 1), ("static", 1), ("lplb", 2), ("static", 2), ("lplb", 0)):
+        layer.fuse_dispatch = fuse > 0
+        layer.send_ctas = 16 if fuse == 2 else 0
         out = layer.forward(x, idx, w, avail, policy)
         torch.cuda.synchronize()
         assert layer.check() == 0
         err = (out.float() - ref).abs().max() / ref.abs().max()
         assert float(err) < 2e-2, (policy, fuse, float(err))
-    layer.fuse_dispatch = False
+    layer.fuse_dispatch, layer.send_ctas = False, 0
     # the first GEMM alone, row by row, against silu(x Wg^T) * (x Wu^T)
     phys = layer.route(idx, avail, "lplb")
     layer.forward_physical(x, phys, w, upto=3)
