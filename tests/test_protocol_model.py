@@ -2,7 +2,7 @@
 
 import random
 
-from lplb_b200.parallel.protocol_model import Fabric, Rank, run_lockstep
+from lplb_b200.parallel.protocol_model import Fabric, Rank, run_lockstep, two_level_step
 
 
 def _truth(counts, n_elems):
@@ -122,3 +122,52 @@ def test_reset_realigns_epochs_after_a_skipped_launch():
     ranks[1].publish([2, 2], fab)
     fab.deliver_all(ranks)
     assert ranks[0].finish() == ([3, 3], 0) and ranks[1].finish() == ([3, 3], 0)
+
+
+def test_two_level_schedule_gives_every_rank_the_global_sum():
+    rng = random.Random(5)
+    for n, node in ((4, 2), (8, 4), (8, 2)):
+        e = 6
+        ranks = [Rank(r, n, e) for r in range(n)]
+        fab = Fabric(n, e)
+        for _ in range(5):  # several launches: both parities, both levels reused
+            counts = [[rng.randrange(1 << 16) for _ in range(e)] for _ in range(n)]
+            want = _truth(counts, e)
+            for sums, miss in two_level_step(ranks, fab, counts, node, lambda level: fab.deliver_all(ranks, rng)):
+                assert miss == 0 and sums == want
+
+
+def test_two_level_levels_do_not_share_slots():
+    # A level-1 word from a rank must not satisfy (or overwrite) the level-0 wait on that rank.
+    n, node, e = 4, 2, 3
+    ranks = [Rank(r, n, e) for r in range(n)]
+    fab = Fabric(n, e)
+    counts = [[r + 1] * e for r in range(n)]
+    two_level_step(ranks, fab, counts, node)
+    # own level-1 word sits in slot [1][level 1][0]; the level-0 slot of the same source holds the raw counts
+    assert [w & 0xFFFFFFFF for w in ranks[0].recv[1][0][0]] == [1] * e
+    assert [w & 0xFFFFFFFF for w in ranks[0].recv[1][1][0]] == [3] * e  # node sum of ranks 0 and 1
+    assert [w & 0xFFFFFFFF for w in ranks[0].recv[1][1][2]] == [7] * e  # node sum of ranks 2 and 3
+
+
+def test_two_level_late_rank_is_reported_by_its_node_and_sums_stay_consistent_across_nodes():
+    # Rank 3's level-0 words to its node peer (rank 2) are held back.  Rank 2 reports it and
+    # substitutes its own counts; the other node sees no timeout and receives rank 2's node
+    # sum, so all ranks except the late one agree on a total.
+    n, node, e = 4, 2, 2
+    ranks = [Rank(r, n, e) for r in range(n)]
+    fab = Fabric(n, e)
+    counts = [[1] * e, [2] * e, [4] * e, [8] * e]
+
+    def deliver(level):
+        for key in fab.pending():
+            if level == 0 and key[0] == 3 and key[1] == 2:
+                continue
+            while fab.queues[key]:
+                fab.deliver(key, ranks)
+
+    res = two_level_step(ranks, fab, counts, node, deliver)
+    assert res[2] == ([1 + 2 + 4 + 4] * e, 0b1000)
+    assert res[0] == ([1 + 2 + 4 + 4] * e, 0)       # partner of rank 2 in the other node
+    assert res[1] == ([1 + 2 + 4 + 8] * e, 0)       # partner of rank 3, whose own node sum was complete
+    assert res[3] == ([1 + 2 + 4 + 8] * e, 0)
