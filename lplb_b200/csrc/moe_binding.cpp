@@ -235,6 +235,24 @@ class MoeEngine {
   }
   int64_t epoch() const { return epoch_; }
 
+  // Back to the state after open(): launch number 0, all epoch-tagged words, flags, arrival
+  // counters and the status block of this rank cleared.  For use after a timeout, when the
+  // ranks no longer agree on how many rows or flags were delivered.  Every rank must call it
+  // with none of the layer's kernels in flight anywhere, and no rank may launch again before
+  // all have returned (the Python layer puts a barrier on either side).
+  void reset() {
+    MOE_CHECK(ready_, "engine is not open");
+    c10::cuda::CUDAGuard guard(device_);
+    MOE_CUDA(cudaDeviceSynchronize());
+    MOE_CUDA(cudaMemset(static_cast<char*>(block_) + off_cnt_, 0, block_bytes_ - off_cnt_));
+    plan_.zero_();
+    tickets_.zero_();
+    status_.zero_();
+    workspace_.zero_();
+    epoch_ = 0;
+    MOE_CUDA(cudaDeviceSynchronize());
+  }
+
   // Views of this rank's peer-visible buffers (for tests).
   torch::Tensor recv_x() const {
     auto opts = torch::TensorOptions().dtype(torch::kBFloat16).device(torch::kCUDA, device_);
@@ -310,6 +328,7 @@ void bind_moe(py::module_& m) {
            py::arg("upto") = 5, py::arg("fuse_dispatch") = false)
       .def("set_timeout_us", &MoeEngine::set_timeout_us)
       .def("set_send_ctas", &MoeEngine::set_send_ctas)
+      .def("reset", &MoeEngine::reset)
       .def("status", &MoeEngine::status)
       .def("plan", &MoeEngine::plan)
       .def("act", &MoeEngine::act)

@@ -159,6 +159,17 @@ class MoELayer:
         """First error code raised by the layer's kernels (0 = none); synchronises."""
         return int(self.engine.status()[0])
 
+    def reset(self) -> None:
+        """Re-align the ranks after a timeout: clear every flag, counter and the status block
+        and restart the launch numbering.  Collective: every rank calls it between steps."""
+        if self.group is not None:
+            import torch.distributed as dist
+
+            dist.barrier(group=self.group)
+        self.engine.reset()
+        if self.group is not None:
+            dist.barrier(group=self.group)
+
     # ------------------------------------------------------------------ reference
     def reference_forward(self, x: torch.Tensor, logical_idx: torch.Tensor, weights: torch.Tensor) -> torch.Tensor:
         """Plain PyTorch fp32 evaluation of the same layer on logical experts (single process):

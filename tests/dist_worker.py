@@ -155,6 +155,8 @@ def main():
             dist.all_reduce(hist, group=group)
             mp.update_redundancy_mapping(hist)
             layer.place_weights()
+        if step == 3:
+            layer.reset()  # collective: flags, counters and launch numbers start over on every rank
         avail.zero_()
         layer.fuse_dispatch = step >= 2  # later steps send the rows from inside the first GEMM
         layer.send_ctas = 16 if step >= 3 else 0  # and the last ones from CTAs that run no tiles

@@ -122,6 +122,21 @@ def test_repeated_calls_and_replaced_placement():
     assert layer.check() == 0 and int(layer.engine.epoch()) >= 5
 
 
+def test_reset_restarts_the_launch_numbering_and_the_layer_keeps_working():
+    planner, layer = _layer(256, 128, 16, 2, 512, r2o=ring(8), red=1)
+    avail = torch.zeros(1, dtype=torch.int32, device="cuda")
+    for step in range(6):
+        layer.fuse_dispatch = step % 2 == 1  # the fused dispatch keeps cumulative arrival counters
+        x, idx, w = _inputs(200 + 30 * step, 256, 16, 2, seed=10 + step)
+        if step == 3:
+            layer.reset()
+            assert int(layer.engine.epoch()) == 0 and layer.engine.status().abs().sum().item() == 0
+        out = layer.forward(x, idx, w, avail)
+        ref = layer.reference_forward(x, idx, w).float()
+        assert float((out.float() - ref).abs().max() / ref.abs().max()) < 2e-2
+    assert layer.check() == 0 and int(layer.engine.epoch()) == 3
+
+
 def test_receive_buffer_overflow_is_reported_not_written():
     planner = Planner(cube(), 32 + 16, 32, 8, device="cuda")
     layer = MoELayer(planner, 256, 128, 4, max_tokens=128)  # capacity 512 rows
