@@ -20,7 +20,6 @@ import os
 import statistics
 import subprocess
 import sys
-import threading
 import time
 
 import torch
@@ -47,76 +46,7 @@ def make_indices(step: int, rank: int, device: torch.device) -> torch.Tensor:
     return logits.bfloat16().topk(TOP_K, dim=-1).indices
 
 
-class ClockSampler:
-    """Samples SM clock and throttle reasons through NVML while the timed region runs."""
-
-    def __init__(self, index: int, period_s: float = 0.004):
-        self.index, self.period = index, period_s
-        self.samples: list[int] = []
-        self.reasons: set[str] = set()
-        self.max_mhz = None
-        self._stop = threading.Event()
-        self._thread = None
-        try:
-            import pynvml
-
-            pynvml.nvmlInit()
-            self._nvml = pynvml
-            self._h = pynvml.nvmlDeviceGetHandleByIndex(index)
-            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM)
-        except Exception:
-            self._nvml = None
-
-    def _loop(self):
-        nv = self._nvml
-        names = {
-            0x8: "hw_slowdown",
-            0x40: "hw_thermal_slowdown",
-            0x20: "sw_thermal_slowdown",
-            0x4: "sw_power_cap",
-            0x80: "hw_power_brake_slowdown",
-        }
-        while not self._stop.is_set():
-            try:
-                self.samples.append(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM))
-                mask = nv.nvmlDeviceGetCurrentClocksEventReasons(self._h)
-                for bit, name in names.items():
-                    if mask & bit:
-                        self.reasons.add(name)
-            except Exception:
-                pass
-            time.sleep(self.period)
-
-    def __enter__(self):
-        if self._nvml is not None:
-            self._thread = threading.Thread(target=self._loop, daemon=True)
-            self._thread.start()
-        return self
-
-    def __exit__(self, *exc):
-        self._stop.set()
-        if self._thread is not None:
-            self._thread.join()
-
-    def summary(self) -> dict:
-        if not self.samples:
-            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": ["unsampled"]}
-        return {
-            "sm_mhz": int(statistics.median(self.samples)),
-            "sm_max_mhz": self.max_mhz,
-            "reasons": sorted(self.reasons),
-            "samples": len(self.samples),
-        }
-
-
-def physical_gpu_index(local: int) -> int:
-    vis = os.environ.get("CUDA_VISIBLE_DEVICES")
-    if vis:
-        try:
-            return int(vis.split(",")[local])
-        except (ValueError, IndexError):
-            pass
-    return local
+from lplb_b200.utils.timing import ClockSampler, physical_gpu_index  # noqa: E402
 
 
 def dist_setup(n_gpus: int):

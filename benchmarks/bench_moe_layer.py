@@ -30,6 +30,7 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
 from lplb_b200 import Planner, cube, ring  # noqa: E402
 from lplb_b200.models.moe import MoELayer  # noqa: E402
+from lplb_b200.utils.timing import ClockSampler, physical_gpu_index  # noqa: E402
 
 
 def main():
@@ -85,8 +86,16 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
         return t
 
+    clocks = {}
+
     def run_policy(policy, upto=5):
         """Per-step device ms (max over ranks, mean over steps) and the max/mean rank load."""
+        with ClockSampler(physical_gpu_index(local), period_s=0.002) as sampler:
+            out = _run_policy(policy, upto)
+        clocks[f"{policy}_upto{upto}"] = sampler.summary()
+        return out
+
+    def _run_policy(policy, upto):
         times, loads = [], []
         for s in range(total):
             flush.fill_(s & 255)
@@ -149,6 +158,7 @@ def main():
             "speedup_lplb_vs_none": round(results["none"][0] / lp_ms, 3),
             "speedup_lplb_vs_eplb": round(results["eplb"][0] / lp_ms, 3),
             "status": status,
+            "rank0_clocks_per_run": clocks,
             "timing": "CUDA events per step around route + layer, 256 MiB L2 flush and a barrier before each step",
         }
         print(json.dumps(out))

@@ -1,6 +1,7 @@
 """Device-side timing helpers.
 
-``time_cuda`` brackets each call with CUDA events on the launching stream, after warm-up,
+``ClockSampler`` reads SM clock, power and throttle reasons through NVML (read-only) while a
+timed region runs.  ``time_cuda`` brackets each call with CUDA events on the launching stream, after warm-up,
 optionally evicting L2 between calls, and reports percentiles.  ``bench_kineto`` measures
 named kernels with ``torch.profiler`` and can export a Chrome trace; it covers what the
 reference's test helper of the same name does (reference ``tests/utils.py:46-94``) and
@@ -13,11 +14,13 @@ import contextlib
 import os
 import statistics
 import sys
+import threading
+import time
 from typing import Callable, Sequence
 
 import torch
 
-__all__ = ["L2Flusher", "time_cuda", "bench_kineto", "suppress_output"]
+__all__ = ["L2Flusher", "time_cuda", "bench_kineto", "suppress_output", "ClockSampler", "physical_gpu_index"]
 
 
 @contextlib.contextmanager
@@ -107,3 +110,78 @@ def bench_kineto(
             total_us = ev.cuda_time_total
         out.append(total_us / max(ev.count, 1) * 1e-6)
     return out[0] if single else out
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons through NVML while the timed region runs."""
+
+    def __init__(self, index: int, period_s: float = 0.004):
+        self.index, self.period = index, period_s
+        self.samples: list[int] = []
+        self.reasons: set[str] = set()
+        self.power_w: list[float] = []
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            self._nvml = pynvml
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self._nvml = None
+
+    def _loop(self):
+        nv = self._nvml
+        names = {
+            0x8: "hw_slowdown",
+            0x40: "hw_thermal_slowdown",
+            0x20: "sw_thermal_slowdown",
+            0x4: "sw_power_cap",
+            0x80: "hw_power_brake_slowdown",
+        }
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM))
+                self.power_w.append(nv.nvmlDeviceGetPowerUsage(self._h) / 1000.0)
+                mask = nv.nvmlDeviceGetCurrentClocksEventReasons(self._h)
+                for bit, name in names.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(self.period)
+
+    def __enter__(self):
+        if self._nvml is not None:
+            self._thread = threading.Thread(target=self._loop, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+
+    def summary(self) -> dict:
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": ["unsampled"]}
+        return {
+            "sm_mhz": int(statistics.median(self.samples)),
+            "sm_max_mhz": self.max_mhz,
+            "reasons": sorted(self.reasons),
+            "samples": len(self.samples),
+            "power_w": int(statistics.median(self.power_w)) if self.power_w else None,
+        }
+
+
+def physical_gpu_index(local: int) -> int:
+    vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+    if vis:
+        try:
+            return int(vis.split(",")[local])
+        except (ValueError, IndexError):
+            pass
+    return local
