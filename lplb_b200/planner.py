@@ -238,6 +238,7 @@ class Planner:
 
     def reset_exchange(self) -> None:
         """Collective: re-zero epochs, flags and buffers on every rank (e.g. after a timeout)."""
+        self._anchor = None
         if self._engine is None:
             return
         if self.ep_group is not None:
@@ -499,5 +500,6 @@ class Planner:
             state["phy2log"].int(), state["log2phy"].int(), state["logcnt"].int(), state["log2edge"].int()
         ).to(self.device)
         self.phy2log = self.mapping.phy2log
+        self._anchor = None  # saved iterates belong to the placement that was replaced
         if self._engine is not None:
             self._engine.set_mapping(self.mapping.phy2log, self.mapping.log2phy, self.mapping.log2edge)
