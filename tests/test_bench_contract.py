@@ -28,3 +28,29 @@ def test_bench_defaults_follow_the_contract():
     args = bench.parse_args([])
     assert args.gpus == 1 and args.warmup >= 3 and args.steps > 0 and args.impl == "ours"
     assert bench.N_LOGICAL == 256 and bench.EP_SIZE == 8 and bench.TOKENS_PER_RANK == 4096 and bench.TOP_K == 8
+
+
+def test_clock_sampler_reads_a_fake_nvml(monkeypatch):
+    """The sampler only reads: clock, power and event reasons, through whatever NVML binding is importable."""
+    import sys
+    import time
+    import types
+
+    from lplb_b200.utils.timing import ClockSampler
+
+    calls = []
+    fake = types.ModuleType("pynvml")
+    fake.NVML_CLOCK_SM = 1
+    fake.nvmlInit = lambda: calls.append("init")
+    fake.nvmlDeviceGetHandleByIndex = lambda i: ("gpu", i)
+    fake.nvmlDeviceGetMaxClockInfo = lambda h, kind: 1965
+    fake.nvmlDeviceGetClockInfo = lambda h, kind: 1500
+    fake.nvmlDeviceGetPowerUsage = lambda h: 987_000
+    fake.nvmlDeviceGetCurrentClocksEventReasons = lambda h: 0x4
+    monkeypatch.setitem(sys.modules, "pynvml", fake)
+    with ClockSampler(3, period_s=0.001) as sampler:
+        time.sleep(0.02)
+    out = sampler.summary()
+    assert out["sm_mhz"] == 1500 and out["sm_max_mhz"] == 1965 and out["power_w"] == 987
+    assert out["reasons"] == ["sw_power_cap"] and out["samples"] >= 1
+    assert set(dir(fake)) >= {"nvmlInit"} and calls == ["init"]  # nothing but reads were asked of it
