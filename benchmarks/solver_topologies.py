@@ -1,0 +1,69 @@
+#!/usr/bin/env python
+"""`Planner.solve_probs` latency per topology on one GPU: how the warp-level LP solver scales
+with the group size (8, 16, 32 ranks) and the number of replicas per rank.
+
+Eight logical experts per rank, loads ~ 4096 * max(0, N(1, 0.3)) per expert, one call per
+event pair (so the ~6 us launch + event floor is included), 256 MiB L2 flush between calls.
+
+    python benchmarks/solver_topologies.py [--only hypercube,torus8x4] [--calls 30]
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+from lplb_b200 import Planner, topology  # noqa: E402
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--only", default="ring8,cube,hypercube,torus2x4,torus8x4")
+    ap.add_argument("--calls", type=int, default=30)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--json", default="")
+    args = ap.parse_args()
+    dev = torch.device("cuda", 0)
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
+    rows = []
+    for name in args.only.split(","):
+        r2o = topology.by_name(name)
+        g, d = r2o.shape
+        n_logical = 8 * g
+        planner = Planner(r2o, n_logical + d * g, n_logical, g, device=dev)
+        gen = torch.Generator(device=dev).manual_seed(g * 10 + d)
+        load = ((torch.randn(n_logical, device=dev, generator=gen) * 0.3 + 1).clamp_min(0) * 4096).int()
+        avail = torch.zeros(1, dtype=torch.int32, device=dev)
+        times = []
+        for it in range(args.warmup + args.calls):
+            flush.fill_(it & 255)
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            planner.solve_probs(load, avail)
+            b.record()
+            torch.cuda.synchronize()
+            if it >= args.warmup:
+                times.append(a.elapsed_time(b) * 1e3)
+        status = planner.check_status()
+        rows.append({
+            "topology": name, "group_size": g, "replicas_per_rank": d,
+            "solve_probs_us_p50": round(statistics.median(times), 1),
+            "lp_iterations_last_call": status["lp_iters"],
+            "all_converged": int(avail) == args.warmup + args.calls,
+        })
+        print(json.dumps(rows[-1]))
+    if args.json:
+        os.makedirs(os.path.dirname(os.path.abspath(args.json)), exist_ok=True)
+        with open(args.json, "w") as fh:
+            json.dump({"rows": rows, "timing": "CUDA events around one call, L2 flushed between calls"}, fh, indent=1)
+
+
+if __name__ == "__main__":
+    main()
