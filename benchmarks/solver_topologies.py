@@ -2,10 +2,12 @@
 """`Planner.solve_probs` latency per topology on one GPU: how the warp-level LP solver scales
 with the group size (8, 16, 32 ranks) and the number of replicas per rank.
 
-Eight logical experts per rank, loads ~ 4096 * max(0, N(1, 0.3)) per expert, one call per
-event pair (so the ~6 us launch + event floor is included), 256 MiB L2 flush between calls.
+Eight logical experts per rank; every call sees a fresh load vector, 4096 * max(0, N(1, 0.3))
+per expert times a per-call factor N(1, 0.05) (consecutive batches of one distribution); one
+call per event pair (so the ~6 us launch + event floor is included), 256 MiB L2 flush between
+calls.  Each topology is timed cold and with `warm_start=True`.
 
-    python benchmarks/solver_topologies.py [--only hypercube,torus8x4] [--calls 30]
+    python benchmarks/solver_topologies.py [--only hypercube,torus8x4] [--calls 30] [--modes cold]
 """
 
 from __future__ import annotations
@@ -28,6 +30,7 @@ def main():
     ap.add_argument("--only", default="ring8,cube,hypercube,torus2x4,torus8x4")
     ap.add_argument("--calls", type=int, default=30)
     ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--modes", default="cold,warm", help="cold: warm_start off; warm: warm_start on")
     ap.add_argument("--json", default="")
     args = ap.parse_args()
     dev = torch.device("cuda", 0)
@@ -37,27 +40,31 @@ def main():
         r2o = topology.by_name(name)
         g, d = r2o.shape
         n_logical = 8 * g
-        planner = Planner(r2o, n_logical + d * g, n_logical, g, device=dev)
         gen = torch.Generator(device=dev).manual_seed(g * 10 + d)
-        load = ((torch.randn(n_logical, device=dev, generator=gen) * 0.3 + 1).clamp_min(0) * 4096).int()
-        avail = torch.zeros(1, dtype=torch.int32, device=dev)
-        times = []
-        for it in range(args.warmup + args.calls):
-            flush.fill_(it & 255)
-            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            a.record()
-            planner.solve_probs(load, avail)
-            b.record()
-            torch.cuda.synchronize()
-            if it >= args.warmup:
-                times.append(a.elapsed_time(b) * 1e3)
-        status = planner.check_status()
-        rows.append({
-            "topology": name, "group_size": g, "replicas_per_rank": d,
-            "solve_probs_us_p50": round(statistics.median(times), 1),
-            "lp_iterations_last_call": status["lp_iters"],
-            "all_converged": int(avail) == args.warmup + args.calls,
-        })
+        base = (torch.randn(n_logical, device=dev, generator=gen) * 0.3 + 1).clamp_min(0) * 4096
+        total = args.warmup + args.calls
+        noise = 1 + 0.05 * torch.randn(total, n_logical, device=dev, generator=gen)
+        loads = (base * noise).clamp_min(0).int()
+        row = {"topology": name, "group_size": g, "replicas_per_rank": d}
+        for mode in args.modes.split(","):
+            warm = mode == "warm"
+            planner = Planner(r2o, n_logical + d * g, n_logical, g, device=dev, warm_start=warm)
+            avail = torch.zeros(1, dtype=torch.int32, device=dev)
+            times, iters = [], []
+            for it in range(total):
+                flush.fill_(it & 255)
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                planner.solve_probs(loads[it], avail)
+                b.record()
+                torch.cuda.synchronize()
+                if it >= args.warmup:
+                    times.append(a.elapsed_time(b) * 1e3)
+                    iters.append(planner.check_status()["lp_iters"])
+            row[f"solve_probs_us_p50_{mode}"] = round(statistics.median(times), 1)
+            row[f"lp_iterations_mean_{mode}"] = round(sum(iters) / len(iters), 2)
+            row[f"all_converged_{mode}"] = int(avail) == total
+        rows.append(row)
         print(json.dumps(rows[-1]))
     if args.json:
         os.makedirs(os.path.dirname(os.path.abspath(args.json)), exist_ok=True)
