@@ -252,6 +252,45 @@ def test_fused_run_balances_real_routing():
     assert float(after.max()) <= t_opt * (1 + 1e-3) + 16
 
 
+def test_run_replays_from_a_cuda_graph():
+    """One capture, many replays: the launch number lives on the device, so a replayed launch
+    is indistinguishable from an eager one.  Each replay must redirect the batch that is in
+    the static input buffer at that time, with the quotas of that batch's own LP."""
+    planner = _planner(topology.cube(), 256, 8, 2)
+    gen = torch.Generator("cuda").manual_seed(3)
+    bias = torch.randn(256, device="cuda", generator=gen)
+    batches = [
+        (torch.randn(2048, 256, device="cuda", generator=gen) + bias).bfloat16().topk(8, dim=-1).indices
+        for _ in range(4)
+    ]
+    planner.update_redundancy_mapping(torch.bincount(batches[0].reshape(-1), minlength=256))
+    idx_static = batches[0].clone()
+    out_static = torch.empty_like(idx_static)
+    avail = torch.zeros(1, dtype=torch.int32, device="cuda")
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):  # first launch outside the capture (attribute and occupancy queries)
+        planner.run(idx_static, avail, out=out_static)
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        planner.run(idx_static, avail, out=out_static)
+    calls_before = planner.check_status()["calls"]
+    avail.zero_()
+    for batch in batches:
+        idx_static.copy_(batch)
+        graph.replay()
+        torch.cuda.synchronize()
+        _check_redirect(planner, batch, out_static, planner.last_probs.clone())
+    status = planner.check_status()
+    assert status.ok and status["calls"] == calls_before + len(batches)
+    assert int(avail) == len(batches)
+    # and an eager launch after the replays continues the same launch numbering
+    out = planner.run(batches[1], avail)
+    _check_redirect(planner, batches[1], out, planner.last_probs.clone())
+    assert planner.check_status()["calls"] == calls_before + len(batches) + 1
+
+
 def test_run_reads_and_writes_pinned_host_memory():
     planner = _planner(topology.cube(), 256, 8, 2)
     gen = torch.Generator("cuda").manual_seed(3)
