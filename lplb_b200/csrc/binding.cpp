@@ -89,9 +89,12 @@ class PlannerEngine {
     LPLB_CHECK(phy2log.numel() == (int64_t)n_group_ * g_ * pl, "phy2log has the wrong size");
     LPLB_CHECK(log2phy.dim() == 2 && log2phy.size(0) == e_ && log2phy.size(1) == 2, "log2phy must be [E, 2]");
     LPLB_CHECK(log2edge.numel() == e_, "log2edge must be [E]");
-    phy2log_ = to_dev_i32(phy2log);
-    log2phy_ = to_dev_i32(log2phy);
-    log2edge_ = to_dev_i32(log2edge);
+    // The tables keep their device addresses for the engine's lifetime (a captured CUDA graph
+    // of a launch stays valid across re-placements); new contents are copied in, ordered on
+    // the current stream after the launches already enqueued.
+    store_i32(phy2log_, phy2log);
+    store_i32(log2phy_, log2phy);
+    store_i32(log2edge_, log2edge);
     invalidate_warm_start();  // a new placement is a new LP
   }
 
@@ -371,6 +374,14 @@ class PlannerEngine {
 
   torch::Tensor to_dev_i32(const torch::Tensor& t) const {
     return t.to(torch::Device(torch::kCUDA, device_), torch::kInt32).contiguous().clone();
+  }
+  void store_i32(torch::Tensor& dst, const torch::Tensor& src) const {
+    if (!dst.defined()) {
+      dst = to_dev_i32(src);
+      return;
+    }
+    c10::cuda::CUDAGuard guard(device_);
+    dst.copy_(src.reshape(dst.sizes()));
   }
 
   lplb::ExchangeDesc exchange_desc() const {

@@ -289,6 +289,16 @@ def test_run_replays_from_a_cuda_graph():
     out = planner.run(batches[1], avail)
     _check_redirect(planner, batches[1], out, planner.last_probs.clone())
     assert planner.check_status()["calls"] == calls_before + len(batches) + 1
+    # a new placement is copied into the tables the captured launch already points at
+    old_phy2log = planner.phy2log.clone()
+    skewed = torch.bincount(batches[2].reshape(-1), minlength=256) * torch.arange(1, 257, device="cuda")
+    planner.update_redundancy_mapping(skewed)
+    assert not torch.equal(old_phy2log, planner.phy2log)
+    idx_static.copy_(batches[3])
+    graph.replay()
+    torch.cuda.synchronize()
+    _check_redirect(planner, batches[3], out_static, planner.last_probs.clone())
+    assert planner.check_status().ok
 
 
 def test_run_reads_and_writes_pinned_host_memory():
