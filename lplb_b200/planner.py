@@ -41,6 +41,8 @@ log = logging.getLogger("lplb_b200")
 
 __all__ = ["Planner", "PlannerStatus"]
 
+_NO_RANGE = contextlib.nullcontext()
+
 _ERR_NAMES = {
     0: "ok",
     1: "grid_timeout",
@@ -156,6 +158,7 @@ class Planner:
         self._anchor: dict | None = None  # CPU path only; the engine keeps its own on the device
         self.exchange_node_size = int(exchange_node_size)
         self._host_out: tuple | None = None
+        self._nvtx_on = self.device.type == "cuda" and os.environ.get("LPLB_B200_NVTX") == "1"
 
         self._engine = None
         self._native_solver = False
@@ -383,7 +386,7 @@ class Planner:
         if n_sms is None:
             n_sms = self._default_sms()
         with self._nvtx("lplb_b200.planner.run"):
-            if self._engine is not None and self.comm in ("p2p", "none") and self._native_solver:
+            if self._engine is not None and self._native_solver and self.comm != "nccl":
                 if not idx.is_cuda and out is None:
                     key = (tuple(idx.shape), idx.dtype)
                     if self._host_out is None or self._host_out[0] != key:
@@ -435,9 +438,9 @@ class Planner:
 
     def _nvtx(self, name: str):
         """NVTX range around the hot path when LPLB_B200_NVTX=1 (for timeline profilers)."""
-        if self._engine is not None and os.environ.get("LPLB_B200_NVTX") == "1":
+        if self._nvtx_on:
             return torch.cuda.nvtx.range(name)
-        return contextlib.nullcontext()
+        return _NO_RANGE
 
     def dump_lp(self, workload: torch.Tensor) -> dict[str, Any]:
         """Everything the solver sees for the given (already summed) statistics, on the host:
