@@ -162,6 +162,9 @@ class MoELayer:
     def reset(self) -> None:
         """Re-align the ranks after a timeout: clear every flag, counter and the status block
         and restart the launch numbering.  Collective: every rank calls it between steps."""
+        # this rank's kernels store into the peers' buffers: they must have drained before any
+        # peer clears its own
+        torch.cuda.synchronize(self.device)
         if self.group is not None:
             import torch.distributed as dist
 

@@ -244,6 +244,8 @@ class Planner:
         self._anchor = None
         if self._engine is None:
             return
+        # this rank's launches store into the peers' buffers: drain them before any peer clears its own
+        torch.cuda.synchronize(self.device)
         if self.ep_group is not None:
             torch.distributed.barrier(group=self.ep_group)
         self._engine.reset_exchange()
