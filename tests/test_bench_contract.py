@@ -54,3 +54,24 @@ def test_clock_sampler_reads_a_fake_nvml(monkeypatch):
     assert out["sm_mhz"] == 1500 and out["sm_max_mhz"] == 1965 and out["power_w"] == 987
     assert out["reasons"] == ["sw_power_cap"] and out["samples"] >= 1
     assert set(dir(fake)) >= {"nvmlInit"} and calls == ["init"]  # nothing but reads were asked of it
+
+
+def test_cpu_plumbing_walkthrough_reaches_the_lp_optimum():
+    """The GPU-free walk-through (placement, LP, redirect on 8 simulated ranks) ends at the HiGHS optimum."""
+    import json
+    import os
+    import subprocess
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="")
+    out = subprocess.run(
+        [sys.executable, os.path.join(root, "benchmarks", "cpu_plumbing.py")],
+        capture_output=True, text=True, timeout=300, env=env, cwd=root,
+    )
+    assert out.returncode == 0, out.stderr[-2000:]
+    line = json.loads(out.stdout.strip().splitlines()[-1])
+    ratios = line["max_over_mean"]
+    assert ratios["after_placement"] < ratios["natural_placement"]
+    assert ratios["after_lp_redirect"] <= ratios["lp_optimum_highs"] + 2e-3
+    assert line["ipm_vs_highs_relative_gap"] < 1e-4 and line["groups_converged"] == 1
