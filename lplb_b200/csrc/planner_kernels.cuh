@@ -380,16 +380,22 @@ __device__ __forceinline__ void st_volatile_u64(unsigned long long* p, unsigned 
 // One level of the exchange among the peers first_peer, first_peer + stride, ... (n_peers of
 // them, this rank included): push `mine` into slot [parity][level][my_rank] of each, wait for
 // their words in this rank's buffer, sum.  Adds the ranks that never arrived to `missing`.
+// Counts use 31 bits.  Bit 31 of a vector's first word is the sender's `degraded` mark ("this
+// vector already contains a substituted share"); a vector that arrives with it is summed as
+// it is and its sender is added to `missing` too, so the report reaches every rank that used it.
 __device__ __forceinline__ void exchange_level(const Exchange& ex, uint32_t epoch, int e, int level, int first_peer,
                                                int stride, int n_peers, const int* mine, int* sum,
-                                               unsigned* missing) {
+                                               unsigned* missing, bool degraded) {
   const int parity = epoch & 1;
   const size_t level_base = ((size_t)parity * 2 + level) * ex.n_ranks;
   const unsigned long long tag = (unsigned long long)epoch << 32;
   for (int j = 0; j < n_peers; ++j) {
     const int r = first_peer + j * stride;
     unsigned long long* slot = ex.recv[r] + (level_base + ex.my_rank) * e;
-    for (int i = threadIdx.x; i < e; i += kBlock) st_volatile_u64(&slot[i], tag | (uint32_t)mine[i]);
+    for (int i = threadIdx.x; i < e; i += kBlock) {
+      const uint32_t mark = (degraded && i == 0) ? 0x80000000u : 0u;
+      st_volatile_u64(&slot[i], tag | ((uint32_t)mine[i] & 0x7FFFFFFFu) | mark);
+    }
   }
   const unsigned long long* base = ex.recv[ex.my_rank] + level_base * e;
   // pass 1: wait until every word of this thread's elements carries the epoch
@@ -421,7 +427,9 @@ __device__ __forceinline__ void exchange_level(const Exchange& ex, uint32_t epoc
     for (int j = 0; j < n_peers; ++j) {
       const int r = first_peer + j * stride;
       const bool absent = (miss >> (r & 31)) & 1u;
-      acc += absent ? mine[i] : (int)(uint32_t)ld_volatile_u64(&base[(size_t)r * e + i]);
+      const uint32_t word = (uint32_t)ld_volatile_u64(&base[(size_t)r * e + i]);
+      if (i == 0 && !absent && (word >> 31)) atomicOr(missing, 1u << (r & 31));
+      acc += absent ? mine[i] : (int)(word & 0x7FFFFFFFu);
     }
     sum[i] = acc;
   }
@@ -440,13 +448,14 @@ __device__ __forceinline__ unsigned exchange_counts(const Exchange& ex, uint32_t
   __syncthreads();
   const int s = ex.node_size;
   if (s <= 0 || s >= ex.n_ranks) {
-    exchange_level(ex, epoch, e, 0, 0, 1, ex.n_ranks, mine, sum, &missing);
+    exchange_level(ex, epoch, e, 0, 0, 1, ex.n_ranks, mine, sum, &missing, false);
   } else {
     const int node = ex.my_rank / s, local = ex.my_rank - node * s;
-    exchange_level(ex, epoch, e, 0, node * s, 1, s, mine, sum, &missing);
+    exchange_level(ex, epoch, e, 0, node * s, 1, s, mine, sum, &missing, false);
+    const bool degraded = missing != 0;  // every thread reads it after the level's closing barrier
     for (int i = threadIdx.x; i < e; i += kBlock) mine[i] = sum[i];
     __syncthreads();
-    exchange_level(ex, epoch, e, 1, local, s, ex.n_ranks / s, mine, sum, &missing);
+    exchange_level(ex, epoch, e, 1, local, s, ex.n_ranks / s, mine, sum, &missing, degraded);
   }
   return missing;
 }

@@ -7,7 +7,9 @@ every word of parity ``n & 1`` carries tag ``n`` or a time budget runs out, then
 rank whose words did not arrive in time is reported and replaced by the reader's own counts.
 With a node size the exchange runs in two levels, each with its own slots
 ``[n & 1][level][my_rank]``: first among the ranks of a node, then the node sums among the
-ranks that hold the same position in every node (``two_level_step``).
+ranks that hold the same position in every node (``two_level_step``).  Counts use 31 bits;
+bit 31 of a vector's first word marks a node sum in which a late rank's share was replaced,
+so that the other nodes report the timeout as well.
 
 The model keeps the same state and lets a test decide, store by store, when (or whether)
 each one is delivered: in order, late, twice, or never.  The only ordering assumed of the
@@ -70,14 +72,18 @@ class Rank:
         self.recv = [[[[0] * n_elems for _ in range(n_ranks)] for _ in range(2)] for _ in range(2)]
         self.mine: list[int] = [0] * n_elems
 
-    def publish(self, counts: list[int], fabric: Fabric, level: int = 0, peers=None, bump: bool = True) -> int:
-        """First half of a level: (bump the epoch and) push the words to ``peers`` (default: all)."""
+    def publish(
+        self, counts: list[int], fabric: Fabric, level: int = 0, peers=None, bump: bool = True, degraded: bool = False
+    ) -> int:
+        """First half of a level: (bump the epoch and) push the words to ``peers`` (default: all).
+        ``degraded`` sets bit 31 of the first word: "this vector contains a substituted share"."""
         if bump:
             self.epoch += 1
         self.mine = list(counts)
         for dst in range(self.n_ranks) if peers is None else peers:
             for e, c in enumerate(counts):
-                fabric.send(Store(self.rank, dst, self.epoch & 1, e, (self.epoch << 32) | (c & 0xFFFFFFFF), level))
+                low = (c & 0x7FFFFFFF) | (0x80000000 if degraded and e == 0 else 0)
+                fabric.send(Store(self.rank, dst, self.epoch & 1, e, (self.epoch << 32) | low, level))
         return self.epoch
 
     def ready(self, level: int = 0) -> list[bool]:
@@ -91,8 +97,10 @@ class Rank:
         ok = self.ready(level)
         buf = self.recv[self.epoch & 1][level]
         miss = sum(1 << r for r in peers if not ok[r])
+        # a vector that arrived but carries the degraded mark is used as it is and reported
+        miss |= sum(1 << r for r in peers if ok[r] and buf[r][0] & 0x80000000)
         sums = [
-            sum((buf[src][e] & 0xFFFFFFFF) if ok[src] else self.mine[e] for src in peers)
+            sum((buf[src][e] & 0x7FFFFFFF) if ok[src] else self.mine[e] for src in peers)
             for e in range(self.n_elems)
         ]
         return sums, miss
@@ -128,7 +136,10 @@ def two_level_step(ranks, fabric: Fabric, counts, node_size: int, deliver=None):
     deliver(0)
     node_sums = [r.finish(0, node_peers[r.rank]) for r in ranks]
     for r in ranks:
-        r.publish(node_sums[r.rank][0], fabric, level=1, peers=cross_peers[r.rank], bump=False)
+        r.publish(
+            node_sums[r.rank][0], fabric, level=1, peers=cross_peers[r.rank], bump=False,
+            degraded=node_sums[r.rank][1] != 0,
+        )
     deliver(1)
     out = []
     for r in ranks:

@@ -439,6 +439,18 @@ def test_two_level_exchange_on_one_gpu():
     assert torch.equal(got.cpu(), 2 * (mine.cpu() + neighbour))
     st = planner2.check_status(clear=True)
     assert st["error"] == "peer_timeout" and st["detail"] == 0b100
+    # the other node answers, but marks its sum as degraded (bit 31 of the first word: one of
+    # its ranks was late and replaced): the sum is used as it is and the report is passed on
+    marked = other_node.clone()
+    marked[0] |= -(1 << 31)
+    epoch = eng2.completed_launches() + 1
+    eng2.debug_fill_slot(1, neighbour, epoch, 0)
+    eng2.debug_fill_slot(2, marked, epoch, 1)
+    got = eng2.all_reduce_counts(mine)
+    torch.cuda.synchronize()
+    assert torch.equal(got.cpu(), mine.cpu() + neighbour + other_node)
+    st = planner2.check_status(clear=True)
+    assert st["error"] == "peer_timeout" and st["detail"] == 0b100 and st["timeouts"] == 1
 
 
 def test_exchange_wait_runs_out_and_falls_back():

@@ -150,10 +150,12 @@ def test_two_level_levels_do_not_share_slots():
     assert [w & 0xFFFFFFFF for w in ranks[0].recv[1][1][2]] == [7] * e  # node sum of ranks 2 and 3
 
 
-def test_two_level_late_rank_is_reported_by_its_node_and_sums_stay_consistent_across_nodes():
-    # Rank 3's level-0 words to its node peer (rank 2) are held back.  Rank 2 reports it and
-    # substitutes its own counts; the other node sees no timeout and receives rank 2's node
-    # sum, so all ranks except the late one agree on a total.
+def test_two_level_late_rank_is_reported_in_every_node():
+    # Rank 3's level-0 words to its node peer (rank 2) are held back.  Rank 2 reports it,
+    # substitutes its own counts and marks its node sum as degraded, so its partner in the
+    # other node (rank 0) reports rank 2's vector too.  Rank 3's own node sum was complete,
+    # so ranks 1 and 3 end with the true total and no report: totals can differ between
+    # ranks after a timeout, but no rank uses a substituted share without saying so.
     n, node, e = 4, 2, 2
     ranks = [Rank(r, n, e) for r in range(n)]
     fab = Fabric(n, e)
@@ -167,7 +169,7 @@ def test_two_level_late_rank_is_reported_by_its_node_and_sums_stay_consistent_ac
                 fab.deliver(key, ranks)
 
     res = two_level_step(ranks, fab, counts, node, deliver)
-    assert res[2] == ([1 + 2 + 4 + 4] * e, 0b1000)
-    assert res[0] == ([1 + 2 + 4 + 4] * e, 0)       # partner of rank 2 in the other node
-    assert res[1] == ([1 + 2 + 4 + 8] * e, 0)       # partner of rank 3, whose own node sum was complete
+    assert res[2] == ([1 + 2 + 4 + 4] * e, 0b1100)   # saw the timeout itself (bit 3) and its own degraded word (bit 2)
+    assert res[0] == ([1 + 2 + 4 + 4] * e, 0b0100)   # partner of rank 2: told by the degraded mark
+    assert res[1] == ([1 + 2 + 4 + 8] * e, 0)        # partner of rank 3, whose own node sum was complete
     assert res[3] == ([1 + 2 + 4 + 8] * e, 0)
