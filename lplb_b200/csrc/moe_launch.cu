@@ -31,7 +31,7 @@ PFN_cuTensorMapEncodeTiled_v12000 encode_fn() {
 bool shape_ok(const LayerShape& sh) {
   return sh.n_ranks >= 1 && sh.n_ranks <= kMaxRanks && sh.my_rank >= 0 && sh.my_rank < sh.n_ranks &&
          sh.n_local >= 1 && sh.n_local <= kMaxLocalExperts && sh.hidden % kBN == 0 && sh.hidden % kBK == 0 &&
-         (2 * sh.inter) % kBN == 0 && sh.inter % kBK == 0 && sh.topk >= 1 &&
+         (2 * sh.inter) % kBN == 0 && sh.inter % kBK == 0 && sh.topk >= 1 && sh.topk <= kCombineMaxTopk &&
          (long long)sh.max_tokens * sh.topk < (1 << 20) && sh.capacity > 0 && sh.capacity < (1 << 24);
 }
 

@@ -12,6 +12,7 @@ namespace lplb {
 namespace moe {
 
 constexpr int kSupportThreads = 256;
+constexpr int kCombineMaxTopk = 64;
 
 __device__ __forceinline__ unsigned long long ldv_u64(const unsigned long long* p) {
   unsigned long long v;
@@ -314,21 +315,38 @@ __global__ void __launch_bounds__(kSupportThreads) combine_kernel(const CombineA
   __syncthreads();
   if (!ok) return;
   const int vec_per_row = a.hidden / 8;
+  // Per token: the slots and weights of its pairs go through shared memory once, then every
+  // thread has the rows of up to eight pairs in flight before it starts to accumulate.
+  __shared__ int s_slot[kCombineMaxTopk];
+  __shared__ float s_w[kCombineMaxTopk];
   for (int t = blockIdx.x; t < a.n_tokens; t += gridDim.x) {
+    __syncthreads();
+    for (int k = threadIdx.x; k < a.topk; k += kSupportThreads) {
+      const long long pair = (long long)t * a.topk + k;
+      s_slot[k] = a.pair_slot[pair];
+      s_w[k] = a.weights[pair];
+    }
+    __syncthreads();
     for (int v = threadIdx.x; v < vec_per_row; v += kSupportThreads) {
       float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-      for (int k = 0; k < a.topk; ++k) {
-        const long long pair = (long long)t * a.topk + k;
-        const int slot = a.pair_slot[pair];
-        if (slot < 0) continue;
-        const float w = a.weights[pair];
-        const uint4 raw = __ldcg(reinterpret_cast<const uint4*>(a.comb + (size_t)slot * a.hidden) + v);
-        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+      for (int k0 = 0; k0 < a.topk; k0 += 8) {
+        uint4 raw[8];
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          const float2 f = __bfloat1622float2(h[q]);
-          acc[2 * q] += w * f.x;
-          acc[2 * q + 1] += w * f.y;
+        for (int j = 0; j < 8; ++j) {
+          const int slot = k0 + j < a.topk ? s_slot[k0 + j] : -1;
+          raw[j] = make_uint4(0, 0, 0, 0);
+          if (slot >= 0) raw[j] = __ldcg(reinterpret_cast<const uint4*>(a.comb + (size_t)slot * a.hidden) + v);
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float w = (k0 + j < a.topk && s_slot[k0 + j] >= 0) ? s_w[k0 + j] : 0.f;  // dropped pair: no term
+          const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw[j]);
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const float2 f = __bfloat1622float2(h[q]);
+            acc[2 * q] += w * f.x;
+            acc[2 * q + 1] += w * f.y;
+          }
         }
       }
       uint4 o;
