@@ -193,7 +193,7 @@ def solve_ipm(
     factor_dtype: torch.dtype | None = None,
     anchor: dict | None = None,
     warm_start: bool = False,
-    guard: float = 0.05,
+    guard: float = 0.1,
     snap_mu: float = 1e-3,
 ) -> IpmResult:
     """Batched primal-dual interior-point solve of the compact LP.

@@ -80,7 +80,7 @@ class Planner:
         grid_timeout_us: float = 1e6,
         allow_self_edges: bool = False,
         warm_start: bool = False,
-        warm_guard: float = 0.05,
+        warm_guard: float = 0.1,
         warm_snap_mu: float = 1e-3,
         exchange_node_size: int = 0,
     ) -> None:
