@@ -7,6 +7,11 @@ that is redrawn every 50 steps; everything is seeded per step.  With N < 8 GPUs 
 still covers the 8-rank Cube (``ep_size=8``); the N real ranks each contribute 4096
 tokens and exchange their statistics, so per-GPU work is fixed ("weak" scaling).
 
+The planner runs in the library's default configuration (warm-started LP).  The step
+counter starts so that a bias redraw, with its expert re-placement (untimed slow path) and
+the cold solves that follow it, falls in the middle of the timed steps.  The same steps are
+timed once more with ``warm_start=False`` and reported as ``value_cold_us``.
+
 ``python bench.py --gpus N --steps K --warmup W`` prints one JSON line on rank 0.
 For N > 1 launch through ``python -m torch.distributed.run --nproc-per-node N``.
 ``--impl reference`` runs the unmodified reference from ``baseline/_ref`` instead.
@@ -35,6 +40,16 @@ TOP_K = 8
 BIAS_PERIOD = 50
 PUBLISHED_SOLVER_US = 100.0  # reference README.md:70, solver only, unstated hardware
 METRIC = "planner.run us (device, max over ranks), EP8 Cube, 4096 tokens/rank x top-8"
+
+
+def first_step(steps: int, warmup: int) -> int:
+    """Number of the first (warm-up) step: chosen so that a bias redraw falls in the middle of
+    the timed steps, or after at most 25 of them in a long run."""
+    lead = min(steps // 2, BIAS_PERIOD // 2)
+    start = BIAS_PERIOD - lead - warmup
+    while start < 0:
+        start += BIAS_PERIOD
+    return start
 
 
 def make_indices(step: int, rank: int, device: torch.device) -> torch.Tensor:
@@ -92,19 +107,20 @@ def run_ours(args) -> dict:
 
     rank, world, local, group = dist_setup(args.gpus)
     dev = torch.device("cuda", local)
-    planner = Planner(
-        cube(), N_LOGICAL + RED_PER_RANK * EP_SIZE, N_LOGICAL, EP_SIZE, group, device=dev, comm=args.comm,
-        warm_start=not args.cold,
-    )
+    n_routed = N_LOGICAL + RED_PER_RANK * EP_SIZE
+    extra = {"warm_start": False} if args.cold else {}  # otherwise the library default
+    planner = Planner(cube(), n_routed, N_LOGICAL, EP_SIZE, group, device=dev, comm=args.comm, **extra)
     n_sms = args.n_sms or torch.cuda.get_device_properties(dev).multi_processor_count
     pl = planner.n_local_routed_experts
 
     total_steps = args.warmup + args.steps
-    idx_dev = [make_indices(s, rank, dev) for s in range(total_steps)]
+    step0 = first_step(args.steps, args.warmup) if args.first_step < 0 else args.first_step
+    idx_dev = [make_indices(step0 + s, rank, dev) for s in range(total_steps)]  # position s = step step0 + s
     idx_pinned = [t.cpu().pin_memory() for t in idx_dev]
     out_pinned = torch.empty_like(idx_pinned[0]).pin_memory()
     avail = torch.zeros(1, dtype=torch.int32, device=dev)
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)  # 2x the 126 MB L2
+    redraws_timed = sum(1 for s in range(args.warmup, total_steps) if (step0 + s) % BIAS_PERIOD == 0)
 
     def barrier():
         if group is not None:
@@ -113,38 +129,44 @@ def run_ours(args) -> dict:
             dist.barrier(group=group)
         torch.cuda.synchronize(dev)
 
-    def replace_experts(first_step: int) -> None:
+    def replace_experts(who, pos: int) -> None:
         """Slow path, outside every timed region: re-place experts from the statistics of the
-        first steps of the bias period that starts at `first_step` (summed over ranks)."""
+        first steps of the bias period that starts at position `pos` (summed over ranks)."""
         hist = torch.zeros(N_LOGICAL, dtype=torch.int64, device=dev)
-        for s in range(first_step, min(first_step + 8, total_steps)):
+        for s in range(pos, min(pos + 8, total_steps)):
             hist += torch.bincount(idx_dev[s].reshape(-1), minlength=N_LOGICAL)
         if group is not None:
             import torch.distributed as dist
 
             dist.all_reduce(hist, group=group)
-        planner.update_redundancy_mapping(hist)
+        who.update_redundancy_mapping(hist)
 
-    replace_experts(0)
     sleep_cycles = int(0.012 * torch.cuda.get_device_properties(dev).clock_rate * 1e3) if hasattr(
         torch.cuda.get_device_properties(dev), "clock_rate") else 20_000_000
+    align_src = torch.zeros(N_LOGICAL, dtype=torch.int32, device=dev)
 
-    def timed_chunks(fn):
-        """Run fn(step) for every timed step between CUDA events.  Steps are enqueued in chunks
-        (one bias period at most) behind a ~10 ms device-side sleep, so the host is far ahead of
-        the GPU and host scheduling jitter cannot open gaps inside an event pair."""
+    def timed_chunks(who, fn):
+        """Run fn(position) for every timed step between CUDA events.  Steps are enqueued in
+        chunks (one bias period at most) behind a ~10 ms device-side sleep, so the host is far
+        ahead of the GPU and host scheduling jitter cannot open gaps inside an event pair.  On
+        several GPUs every timed step is preceded, outside its event pair, by one stand-alone
+        statistics exchange: the ranks leave it within an NVLink round trip of each other, so a
+        step is not charged for the time by which the L2 flush of another GPU ran longer."""
         starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
         ends = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+        align = who.comm == "p2p"
         k = 0
         while k < args.steps:
-            step = args.warmup + k
-            if step % BIAS_PERIOD == 0:
-                replace_experts(step)
-            n = min(args.steps - k, BIAS_PERIOD - step % BIAS_PERIOD)
+            pos = args.warmup + k
+            if (step0 + pos) % BIAS_PERIOD == 0:
+                replace_experts(who, pos)
+            n = min(args.steps - k, BIAS_PERIOD - (step0 + pos) % BIAS_PERIOD)
             barrier()
             torch.cuda._sleep(sleep_cycles)
             for j in range(k, k + n):
                 flush.fill_(j & 0xFF)  # evict L2 between timed iterations
+                if align:
+                    who._engine.all_reduce_counts(align_src)
                 starts[j].record()
                 fn(args.warmup + j)
                 ends[j].record()
@@ -154,16 +176,17 @@ def run_ours(args) -> dict:
         return rank_max(ms, group)
 
     # ---- device-timed kernel path -------------------------------------------------------
+    replace_experts(planner, 0)
     for s in range(args.warmup):
         flush.fill_(s & 0xFF)
         planner.run(idx_dev[s], avail, n_sms)
     last_out = {}
 
-    def fused_step(step):
-        last_out["out"] = planner.run(idx_dev[step], avail, n_sms)
+    def fused_step(pos):
+        last_out["out"] = planner.run(idx_dev[pos], avail, n_sms)
 
     with ClockSampler(physical_gpu_index(local)) as clocks:
-        per_step_ms = timed_chunks(fused_step)
+        per_step_ms = timed_chunks(planner, fused_step)
     out = last_out["out"]
     ms_per_step = float(per_step_ms.mean())
     status = planner.check_status()
@@ -186,18 +209,27 @@ def run_ours(args) -> dict:
     balance_after = post_balance(planner, out, group, pl)
     naive = planner.mapping.log2phy[idx_dev[-1].reshape(-1), 0].long()
     balance_before = post_balance(planner, naive, group, pl)
+    mapping_after_timed = planner.state_dict()
+
+    # ---- the same steps with the other warm-start setting ----------------------------------------
+    other = Planner(cube(), n_routed, N_LOGICAL, EP_SIZE, group, device=dev, comm=args.comm,
+                    warm_start=not planner.warm_start)
+    replace_experts(other, 0)
+    for s in range(args.warmup):
+        other.run(idx_dev[s], avail, n_sms)
+    other_ms = float(timed_chunks(other, lambda pos: other.run(idx_dev[pos], avail, n_sms)).mean())
+    warm_us, cold_us = (ms_per_step * 1e3, other_ms * 1e3) if planner.warm_start else (other_ms * 1e3, ms_per_step * 1e3)
 
     # ---- three-launch pipeline with torch.distributed.all_reduce, same inputs ----------------
     staged = Planner(
-        cube(), N_LOGICAL + RED_PER_RANK * EP_SIZE, N_LOGICAL, EP_SIZE, group, device=dev,
-        comm="nccl" if group is not None else "none",
+        cube(), n_routed, N_LOGICAL, EP_SIZE, group, device=dev,
+        comm="nccl" if group is not None else "none", **extra,
     )
-    staged.load_state_dict(planner.state_dict())
+    replace_experts(staged, 0)
     for s in range(args.warmup):
         staged.run_staged(idx_dev[s], avail, n_sms)
-    mapping_before = planner.state_dict()
-    staged_ms = float(timed_chunks(lambda step: staged.run_staged(idx_dev[step], avail, n_sms)).mean())
-    planner.load_state_dict(mapping_before)
+    staged_ms = float(timed_chunks(staged, lambda pos: staged.run_staged(idx_dev[pos], avail, n_sms)).mean())
+    planner.load_state_dict(mapping_after_timed)
 
     # ---- end to end through the public API: pinned H2D, run, D2H, every step -----------------
     idx_stage = torch.empty_like(idx_dev[0])
@@ -250,13 +282,23 @@ def run_ours(args) -> dict:
 
             dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=group)
         if int(flag) == 1:
-            def graph_step(step):
+            def graph_step(pos):
                 graph.replay()
 
-            # every replay reads the static buffer: refill it per chunk boundary is not needed for
-            # timing (the work does not depend on the values), but keep the data realistic
+            # the work does not depend on the values, but keep the data realistic
             idx_static.copy_(idx_dev[args.warmup])
-            graph_ms = float(timed_chunks(graph_step).mean())
+            graph_ms = float(timed_chunks(planner, graph_step).mean())
+
+    # ---- per-phase device times from the kernel's own stamps (median over the timed steps) -------
+    planner.enable_trace(True)
+    rows = []
+    for k in range(min(args.steps, 50)):
+        flush.fill_(k & 0xFF)
+        planner.run(idx_dev[args.warmup + k], avail, n_sms)
+        rows.append(planner.phase_times_us())
+    planner.enable_trace(False)
+    keys = [key for key in rows[0] if all(key in r for r in rows)]
+    phases = {key: round(statistics.median(r[key] for r in rows), 2) for key in keys}
 
     value_us = ms_per_step * 1e3
     result = {
@@ -281,10 +323,16 @@ def run_ours(args) -> dict:
             "parallelism": f"ep8-cube LP over {world} rank(s)",
             "comm": planner.comm,
             "lp_warm_start": planner.warm_start,
+            "planner_configuration": "library defaults" if not args.cold and args.comm == "auto" else "non-default flags",
             "n_sms": n_sms,
             "l2": "256 MiB buffer written between timed iterations",
-            "slow_path": "update_redundancy_mapping runs at every bias redraw (50 steps), between timed chunks",
-            "launch": "timed steps are enqueued behind a 12 ms device sleep so host jitter stays outside the event pairs",
+            "first_step": step0,
+            "bias_redraws_inside_timed_steps": redraws_timed,
+            "slow_path": "update_redundancy_mapping runs at every bias redraw (every 50 steps, one of them inside "
+                         "the timed steps), between timed chunks; the cold solves after it are timed",
+            "launch": "timed steps are enqueued behind a 12 ms device sleep so host jitter stays outside the event "
+                      "pairs; on several GPUs one untimed stand-alone statistics exchange before every start event "
+                      "re-aligns the ranks after the L2 flush",
         },
         "clocks": clocks.summary(),
         "e2e": {
@@ -298,6 +346,8 @@ def run_ours(args) -> dict:
             "with_copy_engine_transfers_us": round(e2e_ms * 1e3, 3),
         },
         "gpu_launches": args.steps * (1 if planner.comm in ("p2p", "none") else 3),
+        "value_warm_us": round(warm_us, 3),
+        "value_cold_us": round(cold_us, 3),
         "staged_nccl_pipeline_us": round(staged_ms * 1e3, 3),
         "cuda_graph_replay_us": None if graph_ms is None else round(graph_ms * 1e3, 3),
         "balance_max_over_mean": {
@@ -306,23 +356,14 @@ def run_ours(args) -> dict:
             "lp_optimum_float64": round(optimum_ratio, 5),
         },
         "lp_iters_last": status["lp_iters"],
+        "lp_gap_last": status["lp_gap"],
         "status": status["error"],
         "p50_us": round(float(per_step_ms.median()) * 1e3, 3),
         "p90_us": round(float(per_step_ms.quantile(0.9)) * 1e3, 3),
         "max_us": round(float(per_step_ms.max()) * 1e3, 3),
         "min_us": round(float(per_step_ms.min()) * 1e3, 3),
+        "phases_us_median": phases,
     }
-    if args.trace:
-        planner.enable_trace(True)
-        rows = []
-        for k in range(min(args.steps, 50)):
-            flush.fill_(k & 0xFF)
-            planner.run(idx_dev[args.warmup + k], avail, n_sms)
-            rows.append(planner.phase_times_us())
-        planner.enable_trace(False)
-        result["phases_us_median"] = {
-            key: round(statistics.median(r[key] for r in rows), 2) for key in rows[0]
-        }
     if group is not None:
         import torch.distributed as dist
 
@@ -331,7 +372,11 @@ def run_ours(args) -> dict:
 
 
 REFERENCE_DRIVER = r'''
-import json, os, sys, time
+import ctypes, json, os, sys, time
+# The reference's extension is linked against the toolkit's nvJitLink; torch brings an older one
+# with the same soname.  Load the newer one first so that both resolve to it.
+if JITLINK:
+    ctypes.CDLL(JITLINK, mode=ctypes.RTLD_GLOBAL)
 sys.path.insert(0, os.path.join(ROOT, "baseline", "_ref"))
 sys.path.insert(0, ROOT)
 import torch
@@ -344,7 +389,8 @@ r2o = torch.tensor([[3, 0, 1, 2, 7, 4, 5, 6], [6, 7, 4, 5, 0, 1, 2, 3]]).T.int()
 planner = Planner(r2o, bench.N_LOGICAL + bench.RED_PER_RANK * bench.EP_SIZE, bench.N_LOGICAL, bench.EP_SIZE, group)
 n_sms = args.n_sms or torch.cuda.get_device_properties(dev).multi_processor_count
 total = args.warmup + args.steps
-idx = [bench.make_indices(s, rank, dev) for s in range(total)]
+step0 = bench.first_step(args.steps, args.warmup)
+idx = [bench.make_indices(step0 + s, rank, dev) for s in range(total)]
 hist = torch.zeros(bench.N_LOGICAL, dtype=torch.int64, device=dev)
 for s in range(min(8, total)):
     hist += torch.bincount(idx[s].reshape(-1), minlength=bench.N_LOGICAL)
@@ -360,6 +406,14 @@ ends = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
 torch.cuda.synchronize()
 with bench.ClockSampler(bench.physical_gpu_index(local)) as clocks:
     for k in range(args.steps):
+        pos = args.warmup + k
+        if (step0 + pos) % bench.BIAS_PERIOD == 0:  # slow path at the bias redraw, outside the event pairs
+            hist.zero_()
+            for s in range(pos, min(pos + 8, total)):
+                hist += torch.bincount(idx[s].reshape(-1), minlength=bench.N_LOGICAL)
+            if group is not None:
+                torch.distributed.all_reduce(hist, group=group)
+            planner.update_redundancy_mapping(hist)
         flush.fill_(k & 0xFF)
         starts[k].record()
         out = planner.run(idx[args.warmup + k], avail, n_sms)
@@ -378,15 +432,29 @@ if rank == 0:
 '''
 
 
+def find_jitlink() -> str:
+    """The toolkit's libnvJitLink.so.12: the copy shipped beside the reference install, else the
+    one next to the nvcc on PATH or under CUDA_HOME; "" if none is found."""
+    import shutil
+
+    candidates = [os.path.join(ROOT, "baseline", "_ref", "_libs", "libnvJitLink.so.12")]
+    for home in (os.environ.get("CUDA_HOME"), os.environ.get("CUDA_PATH")):
+        if home:
+            candidates.append(os.path.join(home, "lib64", "libnvJitLink.so.12"))
+    nvcc = shutil.which("nvcc")
+    if nvcc:
+        candidates.append(os.path.join(os.path.dirname(os.path.dirname(os.path.realpath(nvcc))), "lib64", "libnvJitLink.so.12"))
+    return next((c for c in candidates if os.path.exists(c)), "")
+
+
 def run_reference(argv: list[str]) -> dict:
     """Run the unmodified reference in a child process; report why if it cannot run."""
     ref_dir = os.path.join(ROOT, "baseline", "_ref", "lplb")
     if not os.path.isdir(ref_dir):
         return {"impl": "reference", "unavailable": "baseline/_ref is not installed (offline pip install of the reference checkout was not done)"}
     env = dict(os.environ)
-    env["LD_LIBRARY_PATH"] = "/usr/local/cuda/lib64:" + env.get("LD_LIBRARY_PATH", "")
-    env.setdefault("LPLB_CACHE_PATH", "/tmp/lplb_ref_cache")
-    code = f"ROOT = {ROOT!r}\nARGV = {argv!r}\n" + REFERENCE_DRIVER
+    env.setdefault("LPLB_CACHE_PATH", os.path.join(ROOT, "baseline", "_ref", "_jit_cache"))
+    code = f"ROOT = {ROOT!r}\nARGV = {argv!r}\nJITLINK = {find_jitlink()!r}\n" + REFERENCE_DRIVER
     try:
         proc = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=900)
     except subprocess.TimeoutExpired:
@@ -409,8 +477,9 @@ def parse_args(argv=None):
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--comm", choices=["auto", "p2p", "nccl", "none"], default="auto")
     ap.add_argument("--n-sms", type=int, default=0, help="CTAs used by the planner kernels (default: all SMs)")
-    ap.add_argument("--cold", action="store_true", help="solve every LP from scratch (Planner(warm_start=False))")
-    ap.add_argument("--trace", action="store_true", help="add per-phase device times from the kernel's own stamps")
+    ap.add_argument("--cold", action="store_true", help="headline with Planner(warm_start=False) instead of the default")
+    ap.add_argument("--first-step", type=int, default=-1, help="number of the first warm-up step (default: chosen "
+                    "so that a bias redraw falls inside the timed steps)")
     ap.add_argument("--dump", default="", help="write the per-step device times (us) to this file")
     return ap.parse_args(argv)
 

@@ -8,6 +8,12 @@ nvJitLink run-time compilation and on-disk cubin cache
 
 A fingerprint of the sources is stored next to the binary; ``load()`` uses the existing
 binary when the fingerprint matches and rebuilds otherwise (when a compiler is present).
+
+``LPLB_B200_DEBUG_BOUNDS=1`` selects the bounds-checking variant: the same sources compiled
+with ``-DLPLB_BOUNDS_CHECK`` into a build directory of their own (``_build_bounds/``).  In that
+variant every data-dependent shared- or global-memory index of the planner and MoE support
+kernels is range-checked; a violation is recorded in the status block and the access is
+skipped.  It stands in for a memory checker where none can be run.
 """
 
 from __future__ import annotations
@@ -25,8 +31,12 @@ _ROOT = Path(__file__).resolve().parent
 _CSRC = _ROOT / "csrc"
 # Where the binary and its fingerprint live.  LPLB_B200_CACHE_PATH relocates it (the
 # reference's LPLB_CACHE_PATH does the same for its JIT cache, reference csrc/plugin.cpp:207-214).
+BOUNDS_CHECK = os.environ.get("LPLB_B200_DEBUG_BOUNDS") == "1"
 _BUILD = Path(os.environ["LPLB_B200_CACHE_PATH"]) if os.environ.get("LPLB_B200_CACHE_PATH") else _ROOT / "_build"
 _NAME = "lplb_b200_native"
+if BOUNDS_CHECK:
+    _BUILD = _BUILD.with_name(_BUILD.name + "_bounds")
+    _NAME = "lplb_b200_native_bounds"
 
 SOURCES = [
     "binding.cpp",
@@ -43,7 +53,7 @@ NVCC_FLAGS = [
     "-O3",
     "-std=c++17",
     "--expt-relaxed-constexpr",
-]
+] + (["-DLPLB_BOUNDS_CHECK"] if BOUNDS_CHECK else [])
 
 _module = None
 

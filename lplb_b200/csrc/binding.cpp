@@ -56,7 +56,7 @@ class PlannerEngine {
  public:
   PlannerEngine(int n_group, int g, int d, int ll, int c, int device)
       : n_group_(n_group), g_(g), d_(d), ll_(ll), c_(c), device_(device) {
-    // Groups beyond the warp solver's sizes can still be counted and redirected here; their LP
+    // Groups beyond the device solvers' sizes can still be counted and redirected here; their LP
     // is solved by the caller (see Planner.solve_probs).
     LPLB_CHECK(g >= 1 && d >= 1, "group size and replicas per rank must be positive");
     LPLB_CHECK(ll >= c * d, "local logical experts < replicated experts");
@@ -95,6 +95,21 @@ class PlannerEngine {
     store_i32(phy2log_, phy2log);
     store_i32(log2phy_, log2phy);
     store_i32(log2edge_, log2edge);
+    // log2slot[e] = rank * (D + 1) + bundle: where expert e's count goes in the LP's per-rank
+    // sums (bundle d of the rank for its replicated experts, slot D for the others).
+    {
+      c10::cuda::CUDAGuard guard(device_);
+      auto i64 = torch::TensorOptions().dtype(torch::kInt64).device(torch::kCUDA, device_);
+      const int64_t ranks = (int64_t)n_group_ * g_;
+      auto own = phy2log_.view({ranks, pl}).slice(1, 0, ll_).to(torch::kInt64).reshape({-1});
+      auto sl = torch::arange(ll_, i64);
+      auto code = torch::where(sl < (int64_t)c_ * d_, sl.remainder(d_), torch::full_like(sl, d_));
+      auto slot = (torch::arange(ranks, i64).unsqueeze(1) * (d_ + 1) + code.unsqueeze(0)).reshape({-1});
+      auto table = torch::zeros({e_}, i64);
+      LPLB_CHECK(own.numel() == e_, "phy2log does not hold every logical expert once");
+      table.scatter_(0, own.clamp(0, e_ - 1), slot);
+      store_i32(log2slot_, table);
+    }
     invalidate_warm_start();  // a new placement is a new LP
   }
 
@@ -104,11 +119,13 @@ class PlannerEngine {
     c10::cuda::CUDAGuard dev_guard(device_);
     if (on) {
       LPLB_CHECK(guard > 0 && snap_mu > 0, "guard and snap_mu must be positive");
-      if (!anchor_.defined()) {
+      const int dp = lplb::anchor_dup(g_, d_, prm_.solver);
+      if (!anchor_.defined() || anchor_.size(2) != 4 * dp + 3) {
         auto f64 = torch::TensorOptions().dtype(torch::kFloat64).device(torch::kCUDA, device_);
-        anchor_ = torch::zeros({n_group_, g_, 4 * d_ + 3}, f64);
+        anchor_ = torch::zeros({n_group_, g_, 4 * dp + 3}, f64);
         anchor_valid_ = torch::zeros({n_group_}, status_.options());
       }
+      warm_ = true;
       prm_.anchor = anchor_.data_ptr<double>();
       prm_.anchor_valid = anchor_valid_.data_ptr<int>();
       prm_.guard = guard;
@@ -116,7 +133,28 @@ class PlannerEngine {
     } else {
       prm_.anchor = nullptr;
       prm_.anchor_valid = nullptr;
+      warm_ = false;
     }
+  }
+
+  // Which device solver runs the LPs: "auto" (warp solver up to 8 ranks, thread-block solver
+  // above), "warp" or "block".  The warm-start state is laid out per solver, so it is dropped.
+  void set_solver(const std::string& kind) {
+    int k = kind == "auto" ? lplb::kSolverAuto : kind == "warp" ? lplb::kSolverWarp : kind == "block" ? lplb::kSolverBlock : -1;
+    LPLB_CHECK(k >= 0, "solver must be auto, warp or block, got " << kind);
+    LPLB_CHECK(lplb::resolve_solver(g_, d_, k) > 0, "the " << kind << " solver does not cover " << g_ << " ranks x " << d_ << " replicas");
+    prm_.solver = k;
+    max_cta64_ = max_cta32_ = -1;
+    if (warm_) set_warm_start(true, prm_.guard, prm_.snap_mu);
+    invalidate_warm_start();
+  }
+  // [n_group] int32: 1 where a saved iterate exists (empty tensor when warm starts are off).
+  torch::Tensor warm_start_valid() const {
+    return anchor_valid_.defined() ? anchor_valid_ : torch::zeros({0}, status_.options());
+  }
+  std::string solver() const {
+    const int k = lplb::resolve_solver(g_, d_, prm_.solver);
+    return k == lplb::kSolverWarp ? "warp" : k == lplb::kSolverBlock ? "block" : "none";
   }
   // Forget the saved iterates (next solve of every group starts cold).  Stream-ordered.
   void invalidate_warm_start() {
@@ -148,7 +186,7 @@ class PlannerEngine {
     LPLB_CHECK(workload.is_cuda() && workload.scalar_type() == torch::kInt32 && workload.is_contiguous(),
                "workload must be a contiguous int32 CUDA tensor");
     LPLB_CHECK(workload.numel() == e_, "workload must have " << e_ << " entries, got " << workload.numel());
-    LPLB_CHECK(has_native_solver(), "no warp solver for this group size; use the tensor-op solver");
+    LPLB_CHECK(has_native_solver(), "no device solver for this group size; use the tensor-op solver");
     check_avail(avail);
     c10::cuda::CUDAGuard guard(device_);
     auto probs = torch::empty({n_group_, g_, d_}, probs_.options());
@@ -209,8 +247,9 @@ class PlannerEngine {
     const int is64 = idx.scalar_type() == torch::kInt64;
     LPLB_CHECK(has_native_solver(), "the fused kernel needs a group of at most " << lplb::kMaxGroupSize
                                         << " ranks with at most " << lplb::kMaxDup << " replicas each");
+    LPLB_CHECK(!use_exchange || n_ranks_ <= 32, "the in-kernel exchange covers at most 32 ranks");
     int& limit = is64 ? max_cta64_ : max_cta32_;
-    if (limit < 0) limit = lplb::max_fused_ctas(g_, d_, e_, is64);
+    if (limit < 0) limit = lplb::max_fused_ctas(topo(), prm_.solver, is64);
     LPLB_CHECK(limit > 0, "fused kernel cannot be resident on this device");
     if (n_cta > limit) n_cta = limit;
     torch::Tensor out;
@@ -233,7 +272,7 @@ class PlannerEngine {
                                  probs_.data_ptr<float>(), avail.data_ptr(), avail.scalar_type() == torch::kInt64,
                                  status_.data_ptr<int>(), out.data_ptr(), n_cta, grid_timeout_ns_,
                                  trace_.defined() ? reinterpret_cast<unsigned long long*>(trace_.data_ptr()) : nullptr,
-                                 cooperative_ ? 1 : 0, stream()));
+                                 cooperative_ ? 1 : 0, leader_mode_, stream()));
     return out;
   }
 
@@ -348,12 +387,13 @@ class PlannerEngine {
   // Cooperative launch (default) makes the driver guarantee that all CTAs of the fused kernel
   // are co-resident; an ordinary launch is cheaper but leaves that to the caller.
   void set_cooperative(bool on) { cooperative_ = on; }
+  void set_leader_mode(int mode) { leader_mode_ = mode; }
 
   // Phase stamps of the fused kernel (see fused_run_kernel): off by default.
   void enable_trace(bool on) {
     c10::cuda::CUDAGuard guard(device_);
     if (on && !trace_.defined())
-      trace_ = torch::zeros({8}, torch::TensorOptions().dtype(torch::kInt64).device(torch::kCUDA, device_));
+      trace_ = torch::zeros({16}, torch::TensorOptions().dtype(torch::kInt64).device(torch::kCUDA, device_));
     if (!on) trace_ = torch::Tensor();
   }
   torch::Tensor trace() const { return trace_; }
@@ -363,10 +403,11 @@ class PlannerEngine {
   torch::Tensor last_probs() const { return probs_; }
   torch::Tensor workspace() const { return workspace_; }
   int n_logical() const { return e_; }
-  bool has_native_solver() const { return g_ <= lplb::kMaxGroupSize && d_ <= lplb::kMaxDup; }
+  bool has_native_solver() const { return lplb::resolve_solver(g_, d_, prm_.solver) > 0; }
   int max_fused_ctas(bool is64) {
+    require_mapping();
     c10::cuda::CUDAGuard guard(device_);
-    return lplb::max_fused_ctas(g_, d_, e_, is64);
+    return lplb::max_fused_ctas(topo(), prm_.solver, is64);
   }
 
  private:
@@ -407,13 +448,15 @@ class PlannerEngine {
 
   lplb::TopoDesc topo() const {
     return lplb::TopoDesc{r2o_.data_ptr<int>(),     o2r_.data_ptr<int>(),      phy2log_.data_ptr<int>(),
-                          log2phy_.data_ptr<int>(), log2edge_.data_ptr<int>(), n_group_, g_, d_, ll_, c_};
+                          log2phy_.data_ptr<int>(), log2edge_.data_ptr<int>(), log2slot_.data_ptr<int>(),
+                          n_group_, g_, d_, ll_, c_};
   }
 
   int n_group_, g_, d_, ll_, c_, e_, device_;
   lplb::SolveParams prm_{24, 1e-4};
   unsigned long long peer_timeout_ns_ = 1000000000ull, grid_timeout_ns_ = 1000000000ull;
-  torch::Tensor r2o_, o2r_, phy2log_, log2phy_, log2edge_;
+  torch::Tensor r2o_, o2r_, phy2log_, log2phy_, log2edge_, log2slot_;
+  bool warm_ = false;
   torch::Tensor workspace_, status_, probs_, trace_, anchor_, anchor_valid_;
   int max_cta64_ = -1, max_cta32_ = -1;
   // exchange
@@ -423,6 +466,7 @@ class PlannerEngine {
   int n_ranks_ = 1, my_rank_ = 0, node_size_ = 0;
   bool exchange_open_ = false;
   bool cooperative_ = true;
+  int leader_mode_ = 0;
 };
 
 }  // namespace
@@ -438,6 +482,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def("set_mapping", &PlannerEngine::set_mapping)
       .def("set_params", &PlannerEngine::set_params)
       .def("set_warm_start", &PlannerEngine::set_warm_start)
+      .def("set_solver", &PlannerEngine::set_solver)
+      .def("solver", &PlannerEngine::solver)
+      .def("warm_start_valid", &PlannerEngine::warm_start_valid)
       .def("invalidate_warm_start", &PlannerEngine::invalidate_warm_start)
       .def("count_idx", &PlannerEngine::count_idx)
       .def("solve", &PlannerEngine::solve)
@@ -455,6 +502,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def("close_exchange", &PlannerEngine::close_exchange)
       .def("exchange_open", &PlannerEngine::exchange_open)
       .def("set_cooperative", &PlannerEngine::set_cooperative)
+      .def("set_leader_mode", &PlannerEngine::set_leader_mode)
       .def("set_exchange_nodes", &PlannerEngine::set_exchange_nodes)
       .def("enable_trace", &PlannerEngine::enable_trace)
       .def("trace", &PlannerEngine::trace)

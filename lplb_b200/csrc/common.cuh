@@ -22,6 +22,10 @@ enum StatusWord : int {
   kStLpFail = 5,     // groups that did not converge, cumulative
   kStTimeouts = 6,   // waits that ran out, cumulative
   kStBadIdx = 7,     // out-of-range expert indices seen, cumulative
+  kStGapPpb = 8,     // largest relative duality gap among the groups of the last launch, in 1e-9 units
+  kStBoundsIndex = 9,   // bounds-checking build: the first index that was out of range ...
+  kStBoundsLimit = 10,  // ... the size it was checked against (kStDetail holds the source line) ...
+  kStBoundsCount = 11,  // ... and how many accesses were skipped, cumulative
   kStatusWords = 16
 };
 
@@ -31,7 +35,8 @@ enum ErrCode : int {
   kErrPeerTimeout = 2,   // a peer GPU never published its counts
   kErrLpTimeout = 3,     // the solving CTA never released the result
   kErrBadIndex = 4,      // expert index outside [-1, E)
-  kErrLpNotConverged = 5
+  kErrLpNotConverged = 5,
+  kErrBounds = 6         // bounds-checking build only: an index left its array; the access was skipped
 };
 
 enum Phase : int { kPhCount = 1, kPhExchange = 2, kPhSolve = 3, kPhRedirect = 4 };
@@ -42,6 +47,33 @@ __device__ __forceinline__ void raise_status(int* status, int code, int phase, i
     status[kStDetail] = detail;
   }
 }
+
+// ---- bounds-checking build -----------------------------------------------------------
+// With -DLPLB_BOUNDS_CHECK every data-dependent shared- or global-memory index of the planner
+// and MoE support kernels goes through LPLB_CHECKED: an index outside [0, n) is recorded in the
+// status block (first one: code, phase, source line, index, limit) and the access is skipped;
+// nothing traps.  This stands in for a memory checker on machines where none can be run; the
+// reference's only guard is a device assert on the expert index
+// (reference lplb/resources/csrc-tmpl/minilp.cu:429-430).  Without the macro the check
+// compiles to `true`.
+#ifdef LPLB_BOUNDS_CHECK
+__device__ __forceinline__ bool index_in_range(long long i, long long n, int* status, int phase, int line) {
+  if (i >= 0 && i < n) return true;
+  if (status != nullptr) {
+    if (atomicCAS(&status[kStErr], 0, kErrBounds) == 0) {
+      status[kStPhase] = phase;
+      status[kStDetail] = line;
+      status[kStBoundsIndex] = (int)i;
+      status[kStBoundsLimit] = (int)n;
+    }
+    atomicAdd(&status[kStBoundsCount], 1);
+  }
+  return false;
+}
+#define LPLB_CHECKED(i, n, status, phase) ::lplb::index_in_range((long long)(i), (long long)(n), (status), (phase), __LINE__)
+#else
+#define LPLB_CHECKED(i, n, status, phase) true
+#endif
 
 // ---- memory-order helpers ------------------------------------------------------------
 __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
@@ -80,7 +112,7 @@ __device__ __forceinline__ bool bounded_wait_ge(const uint32_t* flag, uint32_t t
       if ((int32_t)(v - target) >= 0) return true;
       __nanosleep(backoff);
     }
-    if (backoff < 640) backoff <<= 1;
+    if (backoff < 160) backoff <<= 1;
     if (global_timer_ns() - t0 > budget_ns) return false;
   }
 }

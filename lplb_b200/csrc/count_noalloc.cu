@@ -97,13 +97,12 @@ extern "C" int lplb_count_tokens_noalloc(const void* idx, int idx_is64, long lon
   rc = cudaMemsetAsync(scratch, 0, kHeaderBytes, s);
   if (rc != cudaSuccess) return fail((int)rc, err, err_len, "cudaMemsetAsync failed", cudaGetErrorString(rc));
   const size_t smem = sizeof(int) * (size_t)n_logical;
-  if (idx_is64)
-    count_noalloc_kernel<int64_t><<<n_cta, kThreads, smem, s>>>(static_cast<const int64_t*>(idx), n_tokens, n_logical,
-                                                                scratch, counts_out);
-  else
-    count_noalloc_kernel<int32_t><<<n_cta, kThreads, smem, s>>>(static_cast<const int32_t*>(idx), n_tokens, n_logical,
-                                                                scratch, counts_out);
-  rc = cudaGetLastError();
+  // cudaLaunchKernel returns the outcome of this launch itself, so an earlier, unrelated error
+  // that the calling thread has not collected yet is neither reported as ours nor cleared.
+  void* args[] = {const_cast<void**>(&idx), &n_tokens, &n_logical, &scratch, &counts_out};
+  const void* kernel = idx_is64 ? reinterpret_cast<const void*>(&count_noalloc_kernel<int64_t>)
+                                : reinterpret_cast<const void*>(&count_noalloc_kernel<int32_t>);
+  rc = cudaLaunchKernel(kernel, dim3(n_cta), dim3(kThreads), args, smem, s);
   if (rc != cudaSuccess) return fail((int)rc, err, err_len, "kernel launch failed", cudaGetErrorString(rc));
   return 0;
 }

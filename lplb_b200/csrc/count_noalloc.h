@@ -25,6 +25,11 @@
 //   * The current device must be the one that owns the pointers.  The first call on a
 //     device looks up the array's device address once (cudaGetSymbolAddress); make that
 //     first call before any stream capture begins on that device.
+//   * That first call is also a warm-up in a second sense: CUDA loads a library's device
+//     image on first use, and loading is what places the array and the kernel's code in
+//     device memory.  A process that gives all remaining device memory to its own pool must
+//     therefore make one call per device *before* it takes that memory; every later call
+//     leaves the amount of free device memory unchanged.
 //   * All calls on a device share the one array.  Each call re-zeroes the part that has to
 //     start at zero, so leftovers of earlier calls are harmless, but two calls that overlap
 //     on the GPU (different streams, no ordering between them) race on it: order them.

@@ -1,11 +1,16 @@
-// Lock-step warp emulation for running the warp-level LP solver on a CPU.
+// Lock-step warp and thread-block emulation for running the LP solvers on a CPU.
 //
-// When LPLB_HOST_SIM is defined, lp_solver.cuh compiles as plain C++: the CUDA function
-// qualifiers vanish and the warp intrinsics it uses (__shfl_sync, __shfl_xor_sync,
-// __all_sync) are served by 32 host threads that meet at a barrier on every intrinsic.
-// This works because the solver is written so that all 32 lanes issue the same sequence
-// of intrinsics.  The CPU test-suite uses it to check the exact device arithmetic against
-// the float64 oracle without a GPU.  It has no counterpart in the reference.
+// When LPLB_HOST_SIM is defined, lp_solver.cuh and lp_block_solver.cuh compile as plain
+// C++: the CUDA function qualifiers vanish and the intrinsics they use (__shfl_sync,
+// __shfl_xor_sync, __all_sync, __syncwarp, __syncthreads, a named barrier) are served by
+// host threads that meet at a barrier on every intrinsic.  A warp is 32 threads; a block
+// (run_block) is a set of warps that also share a block-wide and a named barrier, with
+// "shared memory" being an ordinary buffer that the caller passes in.  This works because
+// the solvers are written so that all threads that take part in an intrinsic issue the
+// same sequence of them.  The CPU test-suite uses it to check the exact device arithmetic
+// against the float64 oracle without a GPU: a shuffle or barrier behind a thread-dependent
+// condition shows up as a deadlock here, before any GPU run.  It has no counterpart in the
+// reference.
 #pragma once
 #ifdef LPLB_HOST_SIM
 
@@ -15,6 +20,7 @@
 #include <cstdint>
 #include <cstring>
 #include <functional>
+#include <memory>
 #include <mutex>
 #include <thread>
 #include <vector>
@@ -55,8 +61,26 @@ struct Warp {
   int pred[32];
 };
 
+// Barriers of a thread block: all threads, and the first `named_count` threads.
+struct Block {
+  explicit Block(int n_threads) : all(n_threads) {}
+  Barrier all;
+  std::mutex m;
+  std::unique_ptr<Barrier> named;
+  int named_count = 0;
+  Barrier& named_barrier(int count) {
+    std::lock_guard<std::mutex> lk(m);
+    if (!named || named_count != count) {
+      named = std::make_unique<Barrier>(count);
+      named_count = count;
+    }
+    return *named;
+  }
+};
+
 inline thread_local Warp* g_warp = nullptr;
 inline thread_local int g_lane = 0;
+inline thread_local Block* g_block = nullptr;
 
 template <typename T>
 inline T exchange(T v, int src_lane) {
@@ -85,7 +109,29 @@ inline void run_warp(const std::function<void(int)>& fn) {
   for (auto& t : lanes) t.join();
 }
 
+// Run fn(tid) on n_threads (a multiple of 32) lock-stepped threads forming one thread block.
+inline void run_block(int n_threads, const std::function<void(int)>& fn) {
+  const int n_warps = n_threads / 32;
+  std::vector<std::unique_ptr<Warp>> warps;
+  for (int w = 0; w < n_warps; ++w) warps.push_back(std::make_unique<Warp>());
+  Block block(n_threads);
+  std::vector<std::thread> threads;
+  for (int t = 0; t < n_threads; ++t)
+    threads.emplace_back([&, t] {
+      g_warp = warps[t / 32].get();
+      g_lane = t % 32;
+      g_block = &block;
+      fn(t);
+    });
+  for (auto& t : threads) t.join();
+}
+
 }  // namespace lplb_sim
+
+inline void __syncwarp() { lplb_sim::g_warp->barrier.wait(); }
+inline void __syncthreads() { lplb_sim::g_block->all.wait(); }
+// Barrier among the first `count` threads of the block (bar.sync 1, count on the device).
+inline void lplb_sim_named_barrier(int count) { lplb_sim::g_block->named_barrier(count).wait(); }
 
 template <typename T>
 inline T __shfl_sync(unsigned, T v, int src, int width = 32) {

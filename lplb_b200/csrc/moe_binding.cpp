@@ -93,7 +93,7 @@ class MoeEngine {
     pair_slot_ = torch::full({(int64_t)sh_.max_tokens * sh_.topk}, -1, i32);
     send_pair_ = torch::zeros({(int64_t)sh_.max_tokens * sh_.topk}, i32);
     send_target_ = torch::full({(int64_t)sh_.max_tokens * sh_.topk}, -1, i32);
-    status_ = torch::zeros({16}, i32);
+    status_ = torch::zeros({32}, i32);  // see kMoeStatusWords in moe_support.cuh
     MOE_CUDA(cudaDeviceSynchronize());
     cudaIpcMemHandle_t handle;
     MOE_CUDA(cudaIpcGetMemHandle(&handle, block_));

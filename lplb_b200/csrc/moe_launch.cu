@@ -86,6 +86,7 @@ cudaError_t launch_dispatch(const LayerShape& sh, const LayerBuffers& b, const v
   a.dst_row_start = b.plan + 2 * sh.n_local;
   a.by_cta = b.by_cta;
   a.pair_slot = b.pair_slot;
+  a.status = b.status;
   a.ticket = b.tickets + 0;
   a.n_pairs = (long long)n_tokens * sh.topk;
   a.idx_is64 = idx_is64;
@@ -122,6 +123,7 @@ cudaError_t launch_schedule(const LayerShape& sh, const LayerBuffers& b, const v
   a.pair_slot = b.pair_slot;
   a.send_pair = b.send_pair;
   a.send_target = b.send_target;
+  a.status = b.status;
   a.n_pairs = (long long)n_tokens * sh.topk;
   a.idx_is64 = idx_is64;
   a.n_local = sh.n_local;

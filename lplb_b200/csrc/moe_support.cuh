@@ -13,6 +13,10 @@ namespace moe {
 
 constexpr int kSupportThreads = 256;
 constexpr int kCombineMaxTopk = 64;
+// The layer's status block: words 0-7 its own (word 0 = first error), 8-15 the counting
+// kernel's, 16-31 the record of the bounds-checking build (same layout as the planner's block).
+constexpr int kMoeStatusWords = 32;
+constexpr int kMoeBoundsBase = 16;
 
 __device__ __forceinline__ unsigned long long ldv_u64(const unsigned long long* p) {
   unsigned long long v;
@@ -148,6 +152,7 @@ struct ScheduleArgs {
   int* pair_slot;            // [n_pairs] out
   int* send_pair;            // [n_send] out
   int* send_target;          // [n_send] out
+  int* status;
   long long n_pairs;
   int idx_is64, n_local, n_ranks, capacity;
 };
@@ -170,6 +175,7 @@ __global__ void __launch_bounds__(kSupportThreads) schedule_kernel(const Schedul
       const int k = atomicAdd(&cur[e], 1);
       const int row = a.dst_row_start[e] + k;
       const int pos = a.order_base[e] + k;
+      if (!LPLB_CHECKED(pos, a.n_pairs, a.status + kMoeBoundsBase, kPhRedirect)) continue;
       a.send_pair[pos] = (((int)e % a.n_local) << 20) | (int)i;  // local expert index rides along
       if (row < a.capacity) {
         slot = a.send_base[e] + k;
@@ -191,6 +197,7 @@ struct DispatchArgs {
   const int* dst_row_start;          // [P]
   const int* by_cta;                 // [n_cta, P] inclusive prefix rows from the counting kernel
   int* pair_slot;                    // [tokens * topk] out: return slot of every pair, -1 = dropped
+  int* status;
   unsigned* ticket;
   long long n_pairs;
   int idx_is64, topk, hidden, n_local, n_ranks, my_rank, capacity;
@@ -250,11 +257,16 @@ __global__ void __launch_bounds__(kSupportThreads) dispatch_kernel(const Dispatc
       if (e >= 0 && e < P) {
         const int k = atomicAdd(&cur[e], 1);
         const int row = dst_start[e] + k;
-        if (row < a.capacity) {
+        if (row >= 0 && row < a.capacity) {
           const int dr = (int)e / a.n_local;
-          t = (dr << 24) | row;
           slot = send_base[e] + k;
-          a.recv_meta[dr][row] = (a.my_rank << 20) | slot;
+          if (LPLB_CHECKED(dr, a.n_ranks, a.status + kMoeBoundsBase, kPhRedirect) &&
+              LPLB_CHECKED(slot, a.n_pairs, a.status + kMoeBoundsBase, kPhRedirect)) {
+            t = (dr << 24) | row;
+            a.recv_meta[dr][row] = (a.my_rank << 20) | slot;
+          } else {
+            slot = -1;
+          }
         }
       }
       a.pair_slot[i] = slot;
@@ -335,7 +347,8 @@ __global__ void __launch_bounds__(kSupportThreads) combine_kernel(const CombineA
         for (int j = 0; j < 8; ++j) {
           const int slot = k0 + j < a.topk ? s_slot[k0 + j] : -1;
           raw[j] = make_uint4(0, 0, 0, 0);
-          if (slot >= 0) raw[j] = __ldcg(reinterpret_cast<const uint4*>(a.comb + (size_t)slot * a.hidden) + v);
+          if (slot >= 0 && LPLB_CHECKED(slot, (long long)a.n_tokens * a.topk, a.status + kMoeBoundsBase, kPhRedirect))
+            raw[j] = __ldcg(reinterpret_cast<const uint4*>(a.comb + (size_t)slot * a.hidden) + v);
         }
 #pragma unroll
         for (int j = 0; j < 8; ++j) {

@@ -20,6 +20,7 @@ struct TopoDesc {
   const int* phy2log;
   const int* log2phy;
   const int* log2edge;
+  const int* log2slot;  // [E] rank * (d + 1) + bundle of the expert (d = the rank's non-replicated ones)
   int n_group, g, d, ll, c;
 };
 
@@ -35,16 +36,28 @@ struct ExchangeDesc {
 struct SolveParams {
   int max_iters;
   double tol;
-  double* anchor = nullptr;      // warm-start state [n_group][G][4 * D + 3], or null
+  double* anchor = nullptr;      // warm-start state [n_group][G][4 * DP + 3] (DP = anchor_dup(d)), or null
   int* anchor_valid = nullptr;   // [n_group]
   double guard = 0.05;
   double snap_mu = 1e-3;
+  int solver = 0;                // kSolverAuto / kSolverWarp / kSolverBlock
 };
 
-// Largest group size / replicas per rank that the warp solver is instantiated for.
-constexpr int kMaxGroupSize = 32;
-constexpr int kMaxDup = 4;
+// Two device solvers.  The warp solver keeps a group of up to 32 ranks (up to 4 replicas per
+// rank) in one warp's registers; the thread-block solver takes any group of up to
+// kMaxGroupSize ranks with up to kMaxDup replicas per rank, its matrix in shared memory.
+// kSolverAuto picks the warp solver for groups of up to 8 ranks and the block solver above.
+enum SolverKind : int { kSolverAuto = 0, kSolverWarp = 1, kSolverBlock = 2 };
+constexpr int kMaxWarpGroupSize = 32;
+constexpr int kMaxWarpDup = 4;
+constexpr int kMaxGroupSize = 128;
+constexpr int kMaxDup = 8;
 constexpr int kMaxLogicalExperts = 8192;
+
+// The solver that `requested` resolves to for this shape, or -1 when no device solver fits.
+int resolve_solver(int g, int d, int requested);
+// Replica slots per rank in the warm-start state for this shape and solver.
+int anchor_dup(int g, int d, int requested);
 
 size_t planner_workspace_bytes(int n_logical);
 inline size_t exchange_buffer_bytes(int n_ranks, int n_logical) { return sizeof(unsigned long long) * 4 * (size_t)n_ranks * n_logical; }
@@ -71,9 +84,10 @@ cudaError_t launch_exchange(const int* in, int n_logical, const ExchangeDesc& ex
 cudaError_t launch_fused(const void* idx, int idx_is64, long long n, const TopoDesc& topo, const ExchangeDesc& ex,
                          SolveParams prm, void* workspace, float* probs, void* avail, int avail_is64, int* status,
                          void* out, int n_cta, unsigned long long grid_timeout_ns, unsigned long long* trace,
-                         int cooperative, cudaStream_t stream);
+                         int cooperative, int leader_mode, cudaStream_t stream);
 
-// Co-resident CTA limit of the fused kernel for this shape on the current device.
-int max_fused_ctas(int g, int d, int n_logical, int idx_is64);
+// Co-resident CTA limit of the fused kernel for this topology on the current device (0 when the
+// shape has no device solver or its tables do not fit shared memory).
+int max_fused_ctas(const TopoDesc& topo, int solver, int idx_is64);
 
 }  // namespace lplb

@@ -8,6 +8,7 @@
 #pragma once
 
 #include "common.cuh"
+#include "lp_block_solver.cuh"
 #include "lp_solver.cuh"
 
 namespace lplb {
@@ -23,6 +24,7 @@ struct Topo {
   const int* phy2log;   // [NG*G*Pl]
   const int* log2phy;   // [E, 2]   (original, replica or -1)
   const int* log2edge;  // [E]      index into probs[NG*G*D] or -1
+  const int* log2slot;  // [E]      rank * (D + 1) + bundle (D = the rank's non-replicated experts)
   int n_group, g, d, ll, c, pl, e;
 };
 
@@ -69,6 +71,25 @@ __device__ __forceinline__ void histogram_slice(const IdxT* __restrict__ idx, lo
     atomicAdd(&status[kStBadIdx], bad);
     raise_status(status, kErrBadIndex, kPhCount, bad);
   }
+}
+
+// Shared-memory tables of the redirect phase.  The int2 table comes first so that it is 8-byte
+// aligned for every number of experts, odd ones included.
+struct RedirectTables {
+  int2* phys;  // [E] (original, replica or -1)
+  int* total;  // [E] rank-local tokens per expert (during counting: this CTA's counts)
+  int* cur;    // [E] next ordinal to hand out
+  int* quota;  // [E] ordinals that stay on the original (before the LP: the edge ids)
+  int* rest;   // whatever follows the five E-sized int tables
+};
+__device__ __forceinline__ RedirectTables redirect_tables(int* smem, int e) {
+  RedirectTables t;
+  t.phys = reinterpret_cast<int2*>(smem);
+  t.total = smem + 2 * (size_t)e;
+  t.cur = t.total + e;
+  t.quota = t.cur + e;
+  t.rest = t.quota + e;
+  return t;
 }
 
 // Spread `quota` picks evenly over `total` ordinals: ordinal k is a pick iff
@@ -124,20 +145,27 @@ __device__ __forceinline__ long long load_index(const IdxT* p) {
   return (long long)__ldcv(p);
 }
 
+// Issue the loads of the thread's first kKeep indices (slots past the slice read as -1).
 template <typename IdxT>
-__device__ __forceinline__ void histogram_keep(const IdxT* __restrict__ idx, long long begin, long long end, int e,
-                                               int* __restrict__ hist, int* status, long long (&keep)[kKeep]) {
-  int bad = 0;
+__device__ __forceinline__ void load_keep(const IdxT* __restrict__ idx, long long begin, long long end,
+                                          long long (&keep)[kKeep]) {
 #pragma unroll
   for (int j = 0; j < kKeep; ++j) {
     const long long i = begin + threadIdx.x + (long long)j * kBlock;
-    keep[j] = -1;
-    if (i < end) {
-      const long long v = load_index(idx + i);
-      keep[j] = v;
-      if (v >= 0 && v < e) atomicAdd(&hist[v], 1);
-      else if (v != -1) ++bad;
-    }
+    keep[j] = i < end ? load_index(idx + i) : -1;
+  }
+}
+
+// Count the kept indices and whatever the slice holds beyond them.
+template <typename IdxT>
+__device__ __forceinline__ void histogram_keep(const IdxT* __restrict__ idx, long long begin, long long end, int e,
+                                               int* __restrict__ hist, int* status, const long long (&keep)[kKeep]) {
+  int bad = 0;
+#pragma unroll
+  for (int j = 0; j < kKeep; ++j) {
+    const long long v = keep[j];
+    if (v >= 0 && v < e) atomicAdd(&hist[v], 1);
+    else if (v != -1) ++bad;
   }
   for (long long i = begin + threadIdx.x + (long long)kKeep * kBlock; i < end; i += kBlock) {
     const long long v = load_index(idx + i);
@@ -178,10 +206,12 @@ __device__ __forceinline__ void redirect_keep(const IdxT* __restrict__ idx, long
 // finishes last turns the rows into inclusive prefixes over CTAs, so row n_cta-1 is the
 // rank-local total.  No cooperative launch and no spinning: the last arriver is found
 // with a ticket.
+constexpr int kScanBatch = 32;  // rows of a column loaded before any is stored back
+
 template <typename IdxT>
 __global__ void __launch_bounds__(kBlock) count_kernel(const IdxT* __restrict__ idx, long long n, int e,
                                                        int* __restrict__ by_cta, Workspace* ws, int* status) {
-  extern __shared__ int smem[];
+  extern __shared__ __align__(16) int smem[];
   int* hist = smem;
   __shared__ bool last;
   const int p = blockIdx.x, n_cta = gridDim.x;
@@ -196,16 +226,17 @@ __global__ void __launch_bounds__(kBlock) count_kernel(const IdxT* __restrict__ 
   __syncthreads();
   if (!last) return;
   __threadfence();
-  // Column-wise inclusive scan over the CTA rows.  Eight rows are loaded before any of them is
-  // stored back, so the loads of a batch overlap instead of queueing behind the stores.
+  // Column-wise inclusive scan over the CTA rows.  The walk down a column is serial, so its
+  // cost is the number of memory round trips: kScanBatch rows are loaded before any of them is
+  // stored back, and every thread owns its own column, which keeps all of those loads in flight.
   for (int i = threadIdx.x; i < e; i += kBlock) {
     int run = 0;
-    for (int r0 = 0; r0 < n_cta; r0 += 8) {
-      int v[8];
+    for (int r0 = 0; r0 < n_cta; r0 += kScanBatch) {
+      int v[kScanBatch];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) v[j] = r0 + j < n_cta ? __ldcg(&by_cta[(size_t)(r0 + j) * e + i]) : 0;
+      for (int j = 0; j < kScanBatch; ++j) v[j] = r0 + j < n_cta ? __ldcg(&by_cta[(size_t)(r0 + j) * e + i]) : 0;
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
+      for (int j = 0; j < kScanBatch; ++j) {
         run += v[j];
         if (r0 + j < n_cta) by_cta[(size_t)(r0 + j) * e + i] = run;
       }
@@ -215,10 +246,8 @@ __global__ void __launch_bounds__(kBlock) count_kernel(const IdxT* __restrict__ 
 }
 
 // ---------------------------------------------------------------------------------------
-// LP phase shared by the stand-alone solve kernel and the fused kernel.  `bundle` holds the
-// per-rank bundle and fixed loads made by bundle_sums from the group-wide (already summed
-// over ranks) counts.  Each warp carries 32/GP groups; a CTA covers `kWarps * 32/GP` groups
-// per round.
+// LP phase shared by the stand-alone solve kernels and the fused kernel.  `bundle` holds the
+// per-rank bundle and fixed loads made from the group-wide (already summed over ranks) counts.
 // The success counter may be an int32 or an int64 tensor (the reference's README shows
 // int64, its launcher demands int32: reference README.md:32, csrc/plugin.cpp:528-529).
 struct Counter {
@@ -232,24 +261,37 @@ __device__ __forceinline__ void bump(Counter c) {
 
 // Whole-CTA prologue of the LP: fold the per-expert counts into per-rank bundle loads with one
 // load per (rank, slot) spread over all threads, instead of a serial walk by the few lanes that
-// solve.  bundle[rank * (D + 1) + d] = load of the rank's bundle d, [.. + D] = its fixed load.
-// Integer sums, so the result does not depend on the order of the atomics.
+// solve.  bundle[rank * (D + 1) + d] = load of the rank's bundle d, [.. + D] = its fixed load
+// (D = tp.d).  Integer sums, so the result does not depend on the order of the atomics.
 // Only ranks [rank_begin, rank_end) are filled (a CTA of the stand-alone kernel needs its own
 // groups only); `bundle` is indexed by absolute rank.
-template <int D>
 __device__ __forceinline__ void bundle_sums(const int* __restrict__ cnt, const Topo& tp, int* __restrict__ bundle,
-                                            int rank_begin, int rank_end) {
-  const int n_rep = tp.c * D;
-  for (int i = rank_begin * (D + 1) + threadIdx.x; i < rank_end * (D + 1); i += kBlock) bundle[i] = 0;
+                                            int rank_begin, int rank_end, int* status) {
+  const int dd = tp.d, n_rep = tp.c * dd;
+  for (int i = rank_begin * (dd + 1) + threadIdx.x; i < rank_end * (dd + 1); i += kBlock) bundle[i] = 0;
   __syncthreads();
   for (int i = rank_begin * tp.ll + threadIdx.x; i < rank_end * tp.ll; i += kBlock) {
     const int rank = i / tp.ll, sl = i - rank * tp.ll;
-    const int c = cnt[tp.phy2log[(size_t)rank * tp.pl + sl]];
-    if (c) atomicAdd(&bundle[rank * (D + 1) + (sl < n_rep ? sl % D : D)], c);
+    const int log = tp.phy2log[(size_t)rank * tp.pl + sl];
+    if (!LPLB_CHECKED(log, tp.e, status, kPhSolve)) continue;
+    const int c = cnt[log];
+    if (c) atomicAdd(&bundle[rank * (dd + 1) + (sl < n_rep ? sl % dd : dd)], c);
   }
   __syncthreads();
 }
 
+__device__ __forceinline__ void report_group(const IpmOutcome& res, int grp, Counter avail, int* status) {
+  if (res.converged) bump(avail);
+  else {
+    atomicAdd(&status[kStLpFail], 1);
+    raise_status(status, kErrLpNotConverged, kPhSolve, grp);
+  }
+  atomicMax(&status[kStLpIters], res.iters);
+  const double ppb = fmin(fmax(res.gap, 0.0) * 1e9, 2.0e9);
+  atomicMax(&status[kStGapPpb], ppb == ppb ? (int)ppb : 2000000000);
+}
+
+// Warp solver: each warp carries 32/GP groups; a CTA covers `kWarps * 32/GP` groups per round.
 template <int GP, int D>
 __device__ void solve_groups(const int* __restrict__ bundle, const Topo& tp, int first_group, int group_stride,
                              IpmParams prm, float* __restrict__ probs, Counter avail, int* status) {
@@ -272,8 +314,11 @@ __device__ void solve_groups(const int* __restrict__ bundle, const Topo& tp, int
 #pragma unroll
       for (int d = 0; d < D; ++d) {
         w[d] = (double)mine[d];
-        src[d] = tp.r2o[li * D + d];
-        dst[d] = tp.o2r[li * D + d];
+        const int s = tp.r2o[li * D + d], t = tp.o2r[li * D + d];
+        if (LPLB_CHECKED(s, tp.g, status, kPhSolve) && LPLB_CHECKED(t, tp.g, status, kPhSolve)) {
+          src[d] = s;
+          dst[d] = t;
+        }
       }
     }
     double* anchor = nullptr;
@@ -288,45 +333,120 @@ __device__ void solve_groups(const int* __restrict__ bundle, const Topo& tp, int
     if (live) {
 #pragma unroll
       for (int d = 0; d < D; ++d) probs[((size_t)grp * tp.g + li) * D + d] = (float)f[d];
-      if (li == 0) {
-        if (res.converged) bump(avail);
-        else {
-          atomicAdd(&status[kStLpFail], 1);
-          raise_status(status, kErrLpNotConverged, kPhSolve, grp);
-        }
-        atomicMax(&status[kStLpIters], res.iters);
-      }
+      if (li == 0) report_group(res, grp, avail, status);
     }
   }
 }
 
-// Stand-alone solve kernel: one CTA per `kWarps * 32/GP` groups.  `workload` is int32[E],
-// already summed over ranks by the caller.  Also writes the counts divided by their
-// maximum, which the Python API returns next to the shares
-// (reference csrc/plugin.cpp:504-506, :577).
+// Thread-block solver: the whole CTA solves one group at a time.  DP >= tp.d is the
+// instantiated replica count; slots tp.d..DP-1 are self edges of weight zero.  `scratch` is
+// block_solver_smem_bytes(tp.g, DP) of shared memory, 8-byte aligned.
+template <int DP>
+__device__ void solve_groups_block(const int* __restrict__ bundle, const Topo& tp, int first_group, int group_stride,
+                                   IpmParams prm, float* __restrict__ probs, Counter avail, int* status,
+                                   double* scratch) {
+  const int tid = threadIdx.x, dd = tp.d;
+  for (int grp = first_group; grp < tp.n_group; grp += group_stride) {
+    const bool live = tid < tp.g;
+    double w[DP], fixed = 0.0, f[DP];
+    int src[DP], dst[DP];
+#pragma unroll
+    for (int d = 0; d < DP; ++d) {
+      w[d] = 0.0;
+      src[d] = dst[d] = tid;
+    }
+    if (live) {
+      const int* mine = bundle + ((size_t)grp * tp.g + tid) * (dd + 1);
+      fixed = (double)mine[dd];
+#pragma unroll
+      for (int d = 0; d < DP; ++d) {
+        if (d < dd) {
+          w[d] = (double)mine[d];
+          const int s = tp.r2o[tid * dd + d], t = tp.o2r[tid * dd + d];
+          if (LPLB_CHECKED(s, tp.g, status, kPhSolve) && LPLB_CHECKED(t, tp.g, status, kPhSolve)) {
+            src[d] = s;
+            dst[d] = t;
+          }
+        }
+      }
+    }
+    double* anchor = nullptr;
+    int* anchor_valid = nullptr;
+    if (live && prm.anchor != nullptr) {
+      anchor = prm.anchor + ((size_t)grp * tp.g + tid) * (4 * DP + 3);
+      anchor_valid = prm.anchor_valid + grp;
+    }
+    const IpmOutcome res = ipm_solve_block<DP>(tid, tp.g, w, fixed, src, dst, prm, f, anchor, anchor_valid, scratch);
+    if (live) {
+#pragma unroll
+      for (int d = 0; d < DP; ++d)
+        if (d < dd) probs[((size_t)grp * tp.g + tid) * dd + d] = (float)f[d];
+      if (tid == 0) report_group(res, grp, avail, status);
+    }
+    __syncthreads();  // the scratch area is reused by the next group
+  }
+}
+
+// Counts divided by their maximum, which the Python API returns next to the shares
+// (reference csrc/plugin.cpp:504-506, :577).  Called by one CTA.
+__device__ __forceinline__ void normalise_counts(const int* __restrict__ workload, int e, float* __restrict__ normalised) {
+  __shared__ int wmax[kWarps];
+  int m = 0;
+  for (int i = threadIdx.x; i < e; i += kBlock) m = max(m, workload[i]);
+  for (int o = 16; o > 0; o >>= 1) m = max(m, __shfl_xor_sync(0xffffffffu, m, o));
+  if ((threadIdx.x & 31) == 0) wmax[threadIdx.x >> 5] = m;
+  __syncthreads();
+  m = 0;
+  for (int i = 0; i < kWarps; ++i) m = max(m, wmax[i]);
+  const float inv = m > 0 ? 1.f / (float)m : 0.f;
+  for (int i = threadIdx.x; i < e; i += kBlock) normalised[i] = (float)workload[i] * inv;
+  __syncthreads();
+}
+
+// Stand-alone solve kernel, warp solver: one CTA per `kWarps * 32/GP` groups.  `workload` is
+// int32[E], already summed over ranks by the caller.
 template <int GP, int D>
 __global__ void __launch_bounds__(kBlock) solve_kernel(const int* __restrict__ workload, Topo tp, IpmParams prm,
                                                        float* __restrict__ probs, float* __restrict__ normalised,
                                                        Counter avail, int* status) {
-  __shared__ int wmax[kWarps];
   if (blockIdx.x == 0) {
-    int m = 0;
-    for (int i = threadIdx.x; i < tp.e; i += kBlock) m = max(m, workload[i]);
-    for (int o = 16; o > 0; o >>= 1) m = max(m, __shfl_xor_sync(0xffffffffu, m, o));
-    if ((threadIdx.x & 31) == 0) wmax[threadIdx.x >> 5] = m;
-    __syncthreads();
-    m = 0;
-    for (int i = 0; i < kWarps; ++i) m = max(m, wmax[i]);
-    const float inv = m > 0 ? 1.f / (float)m : 0.f;
-    for (int i = threadIdx.x; i < tp.e; i += kBlock) normalised[i] = (float)workload[i] * inv;
-    if (threadIdx.x == 0) status[kStLpIters] = 0;
-    __syncthreads();
+    if (threadIdx.x == 0) status[kStLpIters] = status[kStGapPpb] = 0;
+    normalise_counts(workload, tp.e, normalised);
   }
-  extern __shared__ int bundle[];
+  extern __shared__ __align__(16) int smem[];
+  int* bundle = smem;
   constexpr int kPerCta = kWarps * (32 / GP);
-  bundle_sums<D>(workload, tp, bundle, min(tp.n_group, (int)blockIdx.x * kPerCta) * tp.g,
-                 min(tp.n_group, ((int)blockIdx.x + 1) * kPerCta) * tp.g);
+  bundle_sums(workload, tp, bundle, min(tp.n_group, (int)blockIdx.x * kPerCta) * tp.g,
+              min(tp.n_group, ((int)blockIdx.x + 1) * kPerCta) * tp.g, status);
   solve_groups<GP, D>(bundle, tp, blockIdx.x * kPerCta, gridDim.x * kPerCta, prm, probs, avail, status);
+}
+
+// Stand-alone solve kernel, thread-block solver: one CTA per group (the reference launches
+// one block per group too, reference csrc/plugin.cpp:559-565).
+// Shared memory for the bundle sums plus the slack that lets the solver's scratch area start on
+// a 16-byte boundary whatever precedes the sums.
+__host__ __device__ inline size_t bundle_bytes_aligned(int n_ranks, int d) {
+  return ((sizeof(int) * (size_t)n_ranks * (d + 1)) + 15 + 16) & ~(size_t)15;
+}
+__device__ __forceinline__ double* scratch_after(int* bundle, int n_ranks, int d) {
+  const uintptr_t end = reinterpret_cast<uintptr_t>(bundle + (size_t)n_ranks * (d + 1));
+  return reinterpret_cast<double*>((end + 15) & ~(uintptr_t)15);
+}
+template <int DP>
+__global__ void __launch_bounds__(kBlock) solve_block_kernel(const int* __restrict__ workload, Topo tp, IpmParams prm,
+                                                             float* __restrict__ probs,
+                                                             float* __restrict__ normalised, Counter avail,
+                                                             int* status) {
+  if (blockIdx.x == 0) {
+    if (threadIdx.x == 0) status[kStLpIters] = status[kStGapPpb] = 0;
+    normalise_counts(workload, tp.e, normalised);
+  }
+  extern __shared__ __align__(16) int smem[];
+  int* bundle = smem;
+  double* scratch = scratch_after(bundle, tp.n_group * tp.g, tp.d);
+  const int grp = blockIdx.x;
+  bundle_sums(workload, tp, bundle, grp * tp.g, (grp + 1) * tp.g, status);
+  solve_groups_block<DP>(bundle, tp, grp, gridDim.x, prm, probs, avail, status, scratch);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -337,22 +457,19 @@ __global__ void __launch_bounds__(kBlock) redirect_kernel(const IdxT* __restrict
                                                           const float* __restrict__ probs,
                                                           const int* __restrict__ by_cta, Topo tp,
                                                           IdxT* __restrict__ out) {
-  extern __shared__ int smem[];
+  extern __shared__ __align__(16) int smem[];
   const int e = tp.e, p = blockIdx.x, n_cta = gridDim.x;
-  int* total = smem;
-  int* cur = total + e;
-  int* quota = cur + e;
-  int2* phys = reinterpret_cast<int2*>(quota + e);
+  const RedirectTables tb = redirect_tables(smem, e);
   for (int i = threadIdx.x; i < e; i += kBlock) {
     const int tot = by_cta[(size_t)(n_cta - 1) * e + i];
-    total[i] = tot;
-    cur[i] = p == 0 ? 0 : by_cta[(size_t)(p - 1) * e + i];
-    quota[i] = quota_of(tot, tp.log2edge[i], probs);
-    phys[i] = reinterpret_cast<const int2*>(tp.log2phy)[i];
+    tb.total[i] = tot;
+    tb.cur[i] = p == 0 ? 0 : by_cta[(size_t)(p - 1) * e + i];
+    tb.quota[i] = quota_of(tot, tp.log2edge[i], probs);
+    tb.phys[i] = reinterpret_cast<const int2*>(tp.log2phy)[i];
   }
   __syncthreads();
-  redirect_slice(idx, slice_begin(n, p, n_cta, kBlock), slice_begin(n, p + 1, n_cta, kBlock), e, cur, total, quota,
-                 phys, out);
+  redirect_slice(idx, slice_begin(n, p, n_cta, kBlock), slice_begin(n, p + 1, n_cta, kBlock), e, tb.cur, tb.total,
+                 tb.quota, tb.phys, out);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -362,12 +479,10 @@ __global__ void __launch_bounds__(kBlock) redirect_kernel(const IdxT* __restrict
 // buffer (plain st over NVLink).  An aligned 8-byte store is single-copy atomic, so a
 // reader that sees the epoch in the upper half also sees the count in the lower half; no
 // fence, no separate flag and no second NVLink round trip are needed.  Each thread then
-// polls the words of its own elements in this GPU's memory and sums them.
+// polls the words of its own elements in this GPU's memory and sums them as they arrive.
 // Two receive buffers alternate by epoch parity: a rank can only be one launch ahead of the
 // slowest peer (it needs that peer's words of the current epoch to finish), so the buffer
-// it overwrites is never still being read.  `mine` and `sum` are shared-memory arrays of E
-// ints.  Returns a bit mask of peers that never arrived; their share of the sum is replaced
-// by this rank's own counts.
+// it overwrites is never still being read.
 __device__ __forceinline__ unsigned long long ld_volatile_u64(const unsigned long long* p) {
   unsigned long long v;
   asm volatile("ld.volatile.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
@@ -376,88 +491,157 @@ __device__ __forceinline__ unsigned long long ld_volatile_u64(const unsigned lon
 __device__ __forceinline__ void st_volatile_u64(unsigned long long* p, unsigned long long v) {
   asm volatile("st.volatile.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
 }
+// Two adjacent words in one 16-byte store.  Each 8-byte half carries its own epoch, so it does
+// not matter whether the two halves become visible together.
+__device__ __forceinline__ void st_volatile_u64x2(unsigned long long* p, unsigned long long a, unsigned long long b) {
+  asm volatile("st.volatile.global.v2.u64 [%0], {%1, %2};" ::"l"(p), "l"(a), "l"(b) : "memory");
+}
+
+constexpr int kMaxRanks = 32;     // peers of one exchange (bit masks are 32 bits wide)
+constexpr int kPollChunk = 8;     // peers whose words one thread keeps in flight per polling pass
+constexpr int kSpinsBeforeSleep = 512;
+
+// Shared state of one exchange call.  `recv` is a copy of the peers' buffer addresses in shared
+// memory (filled by exchange_prepare in the shadow of other work), so the exchange itself
+// starts without a dependent global load.
+struct ExchangeShared {
+  unsigned long long* recv[kMaxRanks];
+  unsigned missing;  // peers that never arrived
+  unsigned marked;   // peers whose vector carried the sender's `degraded` mark
+};
+__device__ __forceinline__ void exchange_prepare(const Exchange& ex, ExchangeShared* xs) {
+  if (threadIdx.x < kMaxRanks) xs->recv[threadIdx.x] = (int)threadIdx.x < ex.n_ranks && ex.recv != nullptr ? ex.recv[threadIdx.x] : nullptr;
+  if (threadIdx.x == 0) xs->missing = xs->marked = 0;
+}
 
 // One level of the exchange among the peers first_peer, first_peer + stride, ... (n_peers of
-// them, this rank included): push `mine` into slot [parity][level][my_rank] of each, wait for
-// their words in this rank's buffer, sum.  Adds the ranks that never arrived to `missing`.
-// Counts use 31 bits.  Bit 31 of a vector's first word is the sender's `degraded` mark ("this
-// vector already contains a substituted share"); a vector that arrives with it is summed as
-// it is and its sender is added to `missing` too, so the report reaches every rank that used it.
-__device__ __forceinline__ void exchange_level(const Exchange& ex, uint32_t epoch, int e, int level, int first_peer,
-                                               int stride, int n_peers, const int* mine, int* sum,
-                                               unsigned* missing, bool degraded) {
+// them, this rank included): push `vec` into slot [parity][level][my_rank] of each, wait for
+// their words in this rank's buffer, and replace `vec` by the sum.  Ranks that never arrived go
+// to xs->missing; their share of the sum is this rank's own vector instead.  Counts use 31
+// bits.  Bit 31 of a vector's first word is the sender's `degraded` mark ("this vector already
+// contains a substituted share"); such a vector is summed as it is and its sender goes to
+// xs->marked, which the caller folds into the report once the level has ended.
+// `xtrace` (thread 0 only, may be null) receives four stamps: own pushes issued, first and
+// last word of another peer seen (for element 0), and that last peer's rank.
+__device__ __forceinline__ void exchange_level(const Exchange& ex, ExchangeShared* xs, uint32_t epoch, int e, int level,
+                                               int first_peer, int stride, int n_peers, int* vec, bool degraded,
+                                               int* status, unsigned long long* xtrace) {
   const int parity = epoch & 1;
   const size_t level_base = ((size_t)parity * 2 + level) * ex.n_ranks;
   const unsigned long long tag = (unsigned long long)epoch << 32;
-  for (int j = 0; j < n_peers; ++j) {
-    const int r = first_peer + j * stride;
-    unsigned long long* slot = ex.recv[r] + (level_base + ex.my_rank) * e;
-    for (int i = threadIdx.x; i < e; i += kBlock) {
+  const size_t my_slot = (level_base + ex.my_rank) * e;
+  // ---- push: all peers' stores are issued back to back, nothing waits in between -----------
+  if ((e & 1) == 0) {
+    const int half = e >> 1, items = n_peers * half;
+    for (int it = threadIdx.x; it < items; it += kBlock) {
+      const int j = it / half, pr = it - j * half, r = first_peer + j * stride;
+      if (!LPLB_CHECKED(r, ex.n_ranks, status, kPhExchange)) continue;
+      const uint32_t mark = (degraded && pr == 0) ? 0x80000000u : 0u;
+      st_volatile_u64x2(xs->recv[r] + my_slot + 2 * pr, tag | ((uint32_t)vec[2 * pr] & 0x7FFFFFFFu) | mark,
+                        tag | ((uint32_t)vec[2 * pr + 1] & 0x7FFFFFFFu));
+    }
+  } else {
+    const int items = n_peers * e;
+    for (int it = threadIdx.x; it < items; it += kBlock) {
+      const int j = it / e, i = it - j * e, r = first_peer + j * stride;
+      if (!LPLB_CHECKED(r, ex.n_ranks, status, kPhExchange)) continue;
       const uint32_t mark = (degraded && i == 0) ? 0x80000000u : 0u;
-      st_volatile_u64(&slot[i], tag | ((uint32_t)mine[i] & 0x7FFFFFFFu) | mark);
+      st_volatile_u64(xs->recv[r] + my_slot + i, tag | ((uint32_t)vec[i] & 0x7FFFFFFFu) | mark);
     }
   }
-  const unsigned long long* base = ex.recv[ex.my_rank] + level_base * e;
-  // pass 1: wait until every word of this thread's elements carries the epoch
+  const bool stamping = xtrace != nullptr && threadIdx.x == 0;
+  if (stamping) xtrace[0] = global_timer_ns();
+  __syncthreads();  // every thread has read the `vec` entries it pushes; they may be overwritten now
+  // ---- poll and sum: one pass over all peers per element, kPollChunk loads in flight --------
+  const unsigned long long* base = xs->recv[ex.my_rank] + level_base * e;
   unsigned late = 0;
+  bool seen_any = false;
   const uint64_t t0 = global_timer_ns();
   for (int i = threadIdx.x; i < e; i += kBlock) {
-    for (int j = 0; j < n_peers; ++j) {
-      const int r = first_peer + j * stride;
-      if ((late >> (r & 31)) & 1u) continue;
-      const unsigned long long* word = &base[(size_t)r * e + i];
+    int acc = 0;
+    for (int j0 = 0; j0 < n_peers; j0 += kPollChunk) {
+      const int nj = min(kPollChunk, n_peers - j0);
+      unsigned pend = (1u << nj) - 1u;
+#pragma unroll
+      for (int b = 0; b < kPollChunk; ++b)
+        if (b < nj && ((late >> ((first_peer + (j0 + b) * stride) & 31)) & 1u)) pend &= ~(1u << b);
       uint32_t spins = 0;
-      while ((uint32_t)(ld_volatile_u64(word) >> 32) != epoch) {
-        if ((++spins & 63u) == 0) {
+      while (pend) {
+        unsigned long long v[kPollChunk];
+#pragma unroll
+        for (int b = 0; b < kPollChunk; ++b)
+          if ((pend >> b) & 1u) v[b] = ld_volatile_u64(&base[(size_t)(first_peer + (j0 + b) * stride) * e + i]);
+#pragma unroll
+        for (int b = 0; b < kPollChunk; ++b) {
+          if (((pend >> b) & 1u) && (uint32_t)(v[b] >> 32) == epoch) {
+            const uint32_t word = (uint32_t)v[b];
+            const int r = first_peer + (j0 + b) * stride;
+            acc += (int)(word & 0x7FFFFFFFu);
+            if (i == 0 && (word >> 31)) atomicOr(&xs->marked, 1u << (r & 31));
+            pend &= ~(1u << b);
+            if (stamping && i == 0 && r != ex.my_rank) {
+              const unsigned long long now = global_timer_ns();
+              if (!seen_any) xtrace[1] = now;
+              seen_any = true;
+              xtrace[2] = now;
+              xtrace[3] = (unsigned long long)r;
+            }
+          }
+        }
+        if (pend && (++spins & 63u) == 0) {
           if (global_timer_ns() - t0 > ex.timeout_ns) {
-            late |= 1u << (r & 31);
+#pragma unroll
+            for (int b = 0; b < kPollChunk; ++b)
+              if ((pend >> b) & 1u) late |= 1u << ((first_peer + (j0 + b) * stride) & 31);
             break;
           }
-          __nanosleep(100);
+          if (spins > kSpinsBeforeSleep) __nanosleep(100);
         }
       }
     }
+    vec[i] = acc;
   }
-  if (late) atomicOr(missing, late);
+  if (late) atomicOr(&xs->missing, late);
   __syncthreads();
-  const unsigned miss = *missing;
-  // pass 2: sum; an absent peer contributes this rank's own vector instead of stale data
-  for (int i = threadIdx.x; i < e; i += kBlock) {
-    int acc = 0;
-    for (int j = 0; j < n_peers; ++j) {
-      const int r = first_peer + j * stride;
-      const bool absent = (miss >> (r & 31)) & 1u;
-      const uint32_t word = (uint32_t)ld_volatile_u64(&base[(size_t)r * e + i]);
-      if (i == 0 && !absent && (word >> 31)) atomicOr(missing, 1u << (r & 31));
-      acc += absent ? mine[i] : (int)(word & 0x7FFFFFFFu);
+  const unsigned miss = xs->missing;
+  if (miss) {
+    // Rare path: a peer is absent for at least one element, so it is absent for all of them.
+    // This rank's own vector is still in its own slot of the receive buffer.
+    for (int i = threadIdx.x; i < e; i += kBlock) {
+      const int own = (int)((uint32_t)ld_volatile_u64(&base[(size_t)ex.my_rank * e + i]) & 0x7FFFFFFFu);
+      int acc = 0;
+      for (int j = 0; j < n_peers; ++j) {
+        const int r = first_peer + j * stride;
+        const bool absent = (miss >> (r & 31)) & 1u;
+        const uint32_t word = (uint32_t)ld_volatile_u64(&base[(size_t)r * e + i]);
+        acc += absent ? own : (int)(word & 0x7FFFFFFFu);
+      }
+      vec[i] = acc;
     }
-    sum[i] = acc;
+    __syncthreads();
   }
-  __syncthreads();
 }
 
-// All-reduce over all ranks.  With ex.node_size < n_ranks it runs in two levels, the schedule
-// of a machine whose ranks form nodes of node_size (the reference reduces inside a node over
-// NVLink and between nodes over the network, reference minilp.cu:111-163): first among the
-// ranks of this rank's node, then the node sums among the ranks with the same position in
-// every node; (node_size - 1) + (n_nodes - 1) partners instead of n_ranks - 1.  `mine` is
-// overwritten with the node sum in that case.
-__device__ __forceinline__ unsigned exchange_counts(const Exchange& ex, uint32_t epoch, int e, int* mine, int* sum) {
-  __shared__ unsigned missing;
-  if (threadIdx.x == 0) missing = 0;
-  __syncthreads();
+// All-reduce over all ranks, in place in `vec` (shared memory, E ints).  With ex.node_size <
+// n_ranks it runs in two levels, the schedule of a machine whose ranks form nodes of node_size
+// (the reference reduces inside a node over NVLink and between nodes over the network,
+// reference minilp.cu:111-163): first among the ranks of this rank's node, then the node sums
+// among the ranks with the same position in every node; (node_size - 1) + (n_nodes - 1)
+// partners instead of n_ranks - 1.  Returns a bit mask of the peers that never arrived or sent
+// a marked vector.  exchange_prepare must have run, followed by a block barrier.
+__device__ __forceinline__ unsigned exchange_counts(const Exchange& ex, ExchangeShared* xs, uint32_t epoch, int e,
+                                                    int* vec, int* status, unsigned long long* xtrace) {
   const int s = ex.node_size;
   if (s <= 0 || s >= ex.n_ranks) {
-    exchange_level(ex, epoch, e, 0, 0, 1, ex.n_ranks, mine, sum, &missing, false);
+    exchange_level(ex, xs, epoch, e, 0, 0, 1, ex.n_ranks, vec, false, status, xtrace);
   } else {
     const int node = ex.my_rank / s, local = ex.my_rank - node * s;
-    exchange_level(ex, epoch, e, 0, node * s, 1, s, mine, sum, &missing, false);
-    const bool degraded = missing != 0;  // every thread reads it after the level's closing barrier
-    for (int i = threadIdx.x; i < e; i += kBlock) mine[i] = sum[i];
-    __syncthreads();
-    exchange_level(ex, epoch, e, 1, local, s, ex.n_ranks / s, mine, sum, &missing, degraded);
+    exchange_level(ex, xs, epoch, e, 0, node * s, 1, s, vec, false, status, xtrace);
+    const bool degraded = xs->missing != 0;  // every thread reads it after the level's closing barrier
+    exchange_level(ex, xs, epoch, e, 1, local, s, ex.n_ranks / s, vec, degraded, status,
+                   xtrace != nullptr ? xtrace + 4 : nullptr);
   }
-  return missing;
+  return xs->missing | xs->marked;  // both final: the last level ended with a block barrier
 }
 
 // ---------------------------------------------------------------------------------------
@@ -466,22 +650,23 @@ __device__ __forceinline__ unsigned exchange_counts(const Exchange& ex, uint32_t
 // keeps that kernel's invariant: the totals of the other parity are zero when it ends.
 __global__ void __launch_bounds__(kBlock) exchange_kernel(const int* __restrict__ in, int e, Exchange ex,
                                                           Workspace* ws, int* __restrict__ out, int* status) {
-  extern __shared__ int smem[];
-  int* mine = smem;
-  int* summed = smem + e;
+  extern __shared__ __align__(16) int smem[];
+  __shared__ ExchangeShared xs;
+  int* vec = smem;
   const uint32_t epoch = ld_acquire_gpu(&ws->epoch) + 1;
   int* other = ws_total(ws, (epoch & 1) ^ 1, e);
+  exchange_prepare(ex, &xs);
   for (int i = threadIdx.x; i < e; i += kBlock) {
-    mine[i] = in[i];
+    vec[i] = in[i];
     other[i] = 0;
   }
   __syncthreads();
-  const unsigned miss = exchange_counts(ex, epoch, e, mine, summed);
+  const unsigned miss = exchange_counts(ex, &xs, epoch, e, vec, status, nullptr);
   if (miss && threadIdx.x == 0) {
     atomicAdd(&status[kStTimeouts], 1);
     raise_status(status, kErrPeerTimeout, kPhExchange, (int)miss);
   }
-  for (int i = threadIdx.x; i < e; i += kBlock) out[i] = summed[i];
+  for (int i = threadIdx.x; i < e; i += kBlock) out[i] = vec[i];
   __syncthreads();
   if (threadIdx.x == 0) st_release_gpu(&ws->epoch, epoch);
 }
@@ -489,34 +674,40 @@ __global__ void __launch_bounds__(kBlock) exchange_kernel(const int* __restrict_
 // ---------------------------------------------------------------------------------------
 // Single-launch planner step.  Launched cooperatively so that all CTAs are co-resident.
 //
-//   every CTA : histogram its slice; reserve an ordinal range per expert with one
-//               returning atomicAdd on the rank-local totals; arrive.
-//   CTA 0     : wait for all arrivals; exchange totals with the peers; solve the LPs
-//               (one warp segment per group); publish the shares; raise lp_done.
-//   every CTA : wait for lp_done; turn shares into integer quotas; rewrite its slice.
+//   every CTA   : histogram its slice; reserve an ordinal range per expert with one
+//                 returning atomicAdd on the rank-local totals; take an arrival ticket.
+//   last ticket : that CTA knows that every count is in.  It exchanges the totals with the
+//                 peers, solves the LPs, publishes the shares and raises lp_done.  Nobody polls
+//                 for the arrivals.
+//   every CTA   : wait for lp_done; turn shares into integer quotas; rewrite its slice.
 //
 // The ordinal ranges come from atomics, so which CTA gets which range differs from run
-// to run; quotas are exact regardless.  Shared memory: 5 int arrays of E entries plus the
-// (D + 1) bundle sums per rank.
+// to run; quotas are exact regardless.  Shared memory: the five E-sized redirect tables, the
+// (D + 1) bundle sums per rank, and for GP == 0 the scratch area of the thread-block solver.
+// GP = 8, 16, 32 selects the warp solver for groups of up to GP ranks, GP = 0 the thread-block
+// solver for any group size; D is the instantiated replica count (>= tp.d when GP == 0).
+constexpr int kTraceWords = 16;
+
 template <int GP, int D, typename IdxT>
 __global__ void __launch_bounds__(kBlock) fused_run_kernel(const IdxT* __restrict__ idx, long long n, Topo tp,
                                                            Exchange ex, IpmParams prm, Workspace* ws,
                                                            float* __restrict__ probs, Counter avail, int* status,
                                                            IdxT* __restrict__ out, unsigned long long grid_timeout_ns,
-                                                           unsigned long long* __restrict__ trace) {
-  extern __shared__ int smem[];
+                                                           unsigned long long* __restrict__ trace, int leader_mode) {
+  extern __shared__ __align__(16) int smem[];
   const int e = tp.e, p = blockIdx.x, n_cta = gridDim.x;
-  // Optional phase stamps (globaltimer, ns) written by thread 0 of CTA 0 and by the CTA
-  // that leaves last: 0 start, 1 own slice counted, 2 all CTAs arrived, 3 statistics
-  // exchanged, 4 LPs solved, 5 CTA 0 redirected its slice, 6 last CTA left.
+  // Optional phase stamps (globaltimer, ns): 0 start (CTA 0), 1 CTA 0 counted its slice, 2 the
+  // last count arrived, 3 statistics exchanged, 4 LPs solved (2-4 by the CTA with the last
+  // ticket), 5 CTA 0 redirected its slice, 6 last CTA left; 8-11 and 12-15 the stamps of the
+  // two exchange levels (see exchange_level).
   const bool tracing = trace != nullptr && threadIdx.x == 0;
   if (tracing && p == 0) trace[0] = global_timer_ns();
-  int* hist = smem;        // this CTA's counts, later the rank-local totals
-  int* cur = hist + e;     // next ordinal to hand out per expert
-  int* quota = cur + e;
-  int2* phys = reinterpret_cast<int2*>(quota + e);
+  const RedirectTables tb = redirect_tables(smem, e);
+  int* hist = tb.total;  // this CTA's counts, later the rank-local totals
   __shared__ uint32_t s_epoch;
   __shared__ int s_ok;
+  __shared__ unsigned s_ticket;
+  __shared__ ExchangeShared xs;
 
   if (threadIdx.x == 0) s_epoch = ld_acquire_gpu(&ws->epoch) + 1;
   for (int i = threadIdx.x; i < e; i += kBlock) hist[i] = 0;
@@ -528,11 +719,9 @@ __global__ void __launch_bounds__(kBlock) fused_run_kernel(const IdxT* __restric
   const long long begin = slice_begin(n, p, n_cta, kBlock), end = slice_begin(n, p + 1, n_cta, kBlock);
   long long keep[kKeep];
   if (p == 0) {
-    // CTA 0 will run the LP: start fetching the tables it gathers from, in the shadow of the
-    // counting phase (they were evicted if anything ran since the last step).
-    const int n_slots = tp.n_group * tp.g * tp.pl;
-    for (int i = threadIdx.x * 32; i < n_slots; i += kBlock * 32)
-      asm volatile("prefetch.global.L2 [%0];" ::"l"(tp.phy2log + i));
+    // Whichever CTA ends up solving will gather from these tables: pull them into L2 in the
+    // shadow of the counting phase (they were evicted if anything ran since the last step).
+    for (int i = threadIdx.x * 32; i < e; i += kBlock * 32) asm volatile("prefetch.global.L2 [%0];" ::"l"(tp.log2slot + i));
     if (threadIdx.x == 0) {
       asm volatile("prefetch.global.L2 [%0];" ::"l"(tp.r2o));
       asm volatile("prefetch.global.L2 [%0];" ::"l"(tp.o2r));
@@ -543,60 +732,92 @@ __global__ void __launch_bounds__(kBlock) fused_run_kernel(const IdxT* __restric
         asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const char*>(prm.anchor) + b));
       if (threadIdx.x == 1) asm volatile("prefetch.global.L2 [%0];" ::"l"(prm.anchor_valid));
     }
-    histogram_keep(idx, begin, end, e, hist, status, keep);
-  } else {
-    histogram_keep(idx, begin, end, e, hist, status, keep);
-    // static lookup tables, fetched while CTA 0 works (quota[] holds the edge ids for now)
-    for (int i = threadIdx.x; i < e; i += kBlock) {
-      quota[i] = tp.log2edge[i];
-      phys[i] = reinterpret_cast<const int2*>(tp.log2phy)[i];
-    }
   }
+  load_keep(idx, begin, end, keep);
+  // static lookup tables, fetched while the indices are on their way (quota[] holds the edge
+  // ids until the shares are known); the peers' buffer addresses likewise
+  for (int i = threadIdx.x; i < e; i += kBlock) {
+    tb.quota[i] = tp.log2edge[i];
+    tb.phys[i] = reinterpret_cast<const int2*>(tp.log2phy)[i];
+  }
+  exchange_prepare(ex, &xs);
+  histogram_keep(idx, begin, end, e, hist, status, keep);
   __syncthreads();
   for (int i = threadIdx.x; i < e; i += kBlock) {
     const int c = hist[i];
-    cur[i] = c ? atomicAdd(&total_g[i], c) : 0;
+    tb.cur[i] = c ? atomicAdd(&total_g[i], c) : 0;
   }
   __threadfence();
   __syncthreads();
-  if (threadIdx.x == 0) atomicAdd(&ws->arrive, 1u);
+  if (threadIdx.x == 0) s_ticket = atomicAdd(&ws->arrive, 1u);
+  if (tracing && p == 0) trace[1] = global_timer_ns();
+  __syncthreads();
 
-  if (p == 0) {
-    if (tracing) trace[1] = global_timer_ns();
-    if (threadIdx.x == 0) {
-      s_ok = bounded_wait_ge<false>(&ws->arrive, (uint32_t)n_cta, grid_timeout_ns);
-      if (tracing) trace[2] = global_timer_ns();
-      if (!s_ok) {
-        atomicAdd(&status[kStTimeouts], 1);
-        raise_status(status, kErrGridTimeout, kPhCount, (int)ld_acquire_gpu(&ws->arrive));
+  bool leader = s_ticket == (unsigned)n_cta - 1;
+  if (leader_mode == 1) {
+    leader = p == 0;
+    if (leader) {
+      if (threadIdx.x == 0) {
+        s_ok = bounded_wait_ge<false>(&ws->arrive, (uint32_t)n_cta, grid_timeout_ns);
+        if (!s_ok) {
+          atomicAdd(&status[kStTimeouts], 1);
+          raise_status(status, kErrGridTimeout, kPhCount, (int)ld_acquire_gpu(&ws->arrive));
+        }
       }
-      status[kStLpIters] = 0;
+      __syncthreads();
     }
-    __syncthreads();
-    int* mine = quota;                           // reuse: local totals
-    int* summed = reinterpret_cast<int*>(phys);  // reuse: group-wide totals (needs E ints of the 2E)
+  }
+  if (leader) {
+    // Every other CTA's counts are in total_g: their atomics precede their tickets.
+    __threadfence();
+    if (tracing) trace[2] = global_timer_ns();
+    if (threadIdx.x == 0) {
+      status[kStLpIters] = 0;
+      status[kStGapPpb] = 0;
+    }
+    int* vec = hist;  // this CTA's own counts are no longer needed: rank-local, then group-wide totals
     int* other = ws_total(ws, parity ^ 1, e);
+    const int first = threadIdx.x;
+    const int first_slot = first < e ? tp.log2slot[first] : 0;  // in flight while the exchange runs
     for (int i = threadIdx.x; i < e; i += kBlock) {
-      mine[i] = __ldcg(&total_g[i]);
+      vec[i] = __ldcg(&total_g[i]);
       other[i] = 0;  // ready for the next launch
     }
     __syncthreads();
     if (ex.n_ranks > 1) {
-      const unsigned miss = exchange_counts(ex, epoch, e, mine, summed);
-      if (miss && threadIdx.x == 0) {
-        atomicAdd(&status[kStTimeouts], 1);
-        raise_status(status, kErrPeerTimeout, kPhExchange, (int)miss);
+      const unsigned miss = exchange_counts(ex, &xs, epoch, e, vec, status, trace != nullptr ? trace + 8 : nullptr);
+      if (miss) {
+        // Shares made from substituted statistics must not become the next warm start, and the
+        // saved iterate may no longer match the peers': this solve and the next one start cold.
+        if (prm.anchor_valid != nullptr)
+          for (int g = threadIdx.x; g < tp.n_group; g += kBlock) prm.anchor_valid[g] = 0;
+        prm.anchor = nullptr;
+        prm.anchor_valid = nullptr;
+        if (threadIdx.x == 0) {
+          atomicAdd(&status[kStTimeouts], 1);
+          raise_status(status, kErrPeerTimeout, kPhExchange, (int)miss);
+        }
       }
-    } else {
-      for (int i = threadIdx.x; i < e; i += kBlock) summed[i] = mine[i];
-      __syncthreads();
     }
-    int* glob = ws_global(ws, e);
-    for (int i = threadIdx.x; i < e; i += kBlock) glob[i] = summed[i];
     if (tracing) trace[3] = global_timer_ns();
-    int* bundle = reinterpret_cast<int*>(phys + e);  // past the five E-sized tables
-    bundle_sums<D>(summed, tp, bundle, 0, tp.n_group * tp.g);
-    solve_groups<GP, D>(bundle, tp, 0, kWarps * (32 / GP), prm, probs, avail, status);
+    // group-wide counts -> per-rank bundle loads, and a copy for the host
+    int* glob = ws_global(ws, e);
+    int* bundle = tb.rest;
+    const int n_bundle = tp.n_group * tp.g * (tp.d + 1);
+    for (int i = threadIdx.x; i < n_bundle; i += kBlock) bundle[i] = 0;
+    __syncthreads();
+    for (int i = threadIdx.x; i < e; i += kBlock) {
+      const int c = vec[i];
+      glob[i] = c;
+      const int slot = i == first ? first_slot : tp.log2slot[i];
+      if (c && LPLB_CHECKED(slot, n_bundle, status, kPhSolve)) atomicAdd(&bundle[slot], c);
+    }
+    __syncthreads();
+    if constexpr (GP == 0) {
+      solve_groups_block<D>(bundle, tp, 0, 1, prm, probs, avail, status, scratch_after(bundle, tp.n_group * tp.g, tp.d));
+    } else {
+      solve_groups<GP, D>(bundle, tp, 0, kWarps * (32 / GP), prm, probs, avail, status);
+    }
     __threadfence();
     __syncthreads();
     if (threadIdx.x == 0) st_release_gpu(&ws->lp_done, epoch);
@@ -614,13 +835,12 @@ __global__ void __launch_bounds__(kBlock) fused_run_kernel(const IdxT* __restric
   const bool have_probs = s_ok;
   for (int i = threadIdx.x; i < e; i += kBlock) {
     const int tot = __ldcg(&total_g[i]);
-    hist[i] = tot;
-    const int edge = p == 0 ? tp.log2edge[i] : quota[i];
-    quota[i] = have_probs ? quota_of(tot, edge, probs) : (edge < 0 ? tot : tot / 2);
-    if (p == 0) phys[i] = reinterpret_cast<const int2*>(tp.log2phy)[i];
+    tb.total[i] = tot;
+    const int edge = tb.quota[i];
+    tb.quota[i] = have_probs ? quota_of(tot, edge, probs) : (edge < 0 ? tot : tot / 2);
   }
   __syncthreads();
-  redirect_keep(idx, begin, end, e, cur, hist, quota, phys, out, keep);
+  redirect_keep(idx, begin, end, e, tb.cur, tb.total, tb.quota, tb.phys, out, keep);
 
   __syncthreads();
   if (tracing && p == 0) trace[5] = global_timer_ns();

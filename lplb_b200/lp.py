@@ -229,6 +229,7 @@ def solve_ipm(
     if squeeze:
         w, fixed = w.unsqueeze(0), fixed.unsqueeze(0)
     nb = w.shape[0]
+    dev = w.device  # every tensor below lives where the data lives (CPU oracle or the planner's GPU)
     w = w.to(dtype)
     fixed = fixed.to(dtype)
     scale = (w.sum((-1, -2)) + fixed.sum(-1)) / g
@@ -236,21 +237,21 @@ def solve_ipm(
     scale = torch.where(empty, torch.ones_like(scale), scale)
     m, base = compact_form(w / scale.view(nb, 1, 1), fixed / scale.view(nb, 1), r2o)
     mt = m.transpose(1, 2)
-    one = torch.ones(nb, g, 1, dtype=dtype)
+    one = torch.ones(nb, g, 1, dtype=dtype, device=dev)
     fdt = factor_dtype or dtype
 
-    f = torch.full((nb, k), 0.5, dtype=dtype)
-    v = torch.full((nb, k), 0.5, dtype=dtype)
+    f = torch.full((nb, k), 0.5, dtype=dtype, device=dev)
+    v = torch.full((nb, k), 0.5, dtype=dtype, device=dev)
     load = base + (m @ f.unsqueeze(-1)).squeeze(-1)
     spread = load.max(1).values - load.min(1).values
     t = load.max(1).values + 0.5 * spread + 0.05
     s = t.unsqueeze(1) - load
-    y = torch.full((nb, g), 1.0 / g, dtype=dtype)
+    y = torch.full((nb, g), 1.0 / g, dtype=dtype, device=dev)
     mu0 = (s * y).sum(1, keepdim=True) / g
     z = (mu0 / 0.5).expand(nb, k).clone()
     q = z.clone()
 
-    use_warm = torch.zeros(nb, dtype=torch.bool)
+    use_warm = torch.zeros(nb, dtype=torch.bool, device=dev)
     if warm_start and anchor is not None:
         fa, va = anchor["f"].to(dtype), anchor["v"].to(dtype)
         sa, ta = anchor["s"].to(dtype), anchor["t"].to(dtype)
@@ -267,21 +268,21 @@ def solve_ipm(
             new_anchor = {key: val.clone() for key, val in anchor.items()}
         else:
             new_anchor = {
-                "f": torch.zeros(nb, k, dtype=dtype), "v": torch.zeros(nb, k, dtype=dtype),
-                "z": torch.zeros(nb, k, dtype=dtype), "q": torch.zeros(nb, k, dtype=dtype),
-                "s": torch.zeros(nb, g, dtype=dtype), "y": torch.zeros(nb, g, dtype=dtype),
-                "t": torch.zeros(nb, dtype=dtype), "valid": torch.zeros(nb, dtype=torch.bool),
+                "f": torch.zeros(nb, k, dtype=dtype, device=dev), "v": torch.zeros(nb, k, dtype=dtype, device=dev),
+                "z": torch.zeros(nb, k, dtype=dtype, device=dev), "q": torch.zeros(nb, k, dtype=dtype, device=dev),
+                "s": torch.zeros(nb, g, dtype=dtype, device=dev), "y": torch.zeros(nb, g, dtype=dtype, device=dev),
+                "t": torch.zeros(nb, dtype=dtype, device=dev), "valid": torch.zeros(nb, dtype=torch.bool, device=dev),
             }
-    saved = torch.zeros(nb, dtype=torch.bool)
+    saved = torch.zeros(nb, dtype=torch.bool, device=dev)
     # the feasible iterate with the smallest gap seen so far: what is returned if the loop
     # ends without meeting `tol` (a tolerance below what float arithmetic can certify)
-    best_gap = torch.full((nb,), float("inf"), dtype=dtype)
+    best_gap = torch.full((nb,), float("inf"), dtype=dtype, device=dev)
     best_f = f.clone()
-    stopped = torch.zeros(nb, dtype=torch.bool)
+    stopped = torch.zeros(nb, dtype=torch.bool, device=dev)
 
     done = empty.clone()
-    iters = torch.zeros(nb, dtype=torch.int64)
-    gap = torch.where(empty, torch.zeros(nb, dtype=dtype), torch.full((nb,), float("inf"), dtype=dtype))
+    iters = torch.zeros(nb, dtype=torch.int64, device=dev)
+    gap = torch.where(empty, torch.zeros(nb, dtype=dtype, device=dev), torch.full((nb,), float("inf"), dtype=dtype, device=dev))
     eta = 0.995
     n_comp = g + 2 * k
 
@@ -321,7 +322,7 @@ def solve_ipm(
 
         theta = 1.0 / (z / f + q / v)
         n = (m * theta.unsqueeze(1)) @ mt + torch.diag_embed(s / y)
-        n = torch.where(done.view(nb, 1, 1), torch.eye(g, dtype=dtype).expand(nb, g, g), n)
+        n = torch.where(done.view(nb, 1, 1), torch.eye(g, dtype=dtype, device=dev).expand(nb, g, g), n)
         chol = _chol_factor(n.to(fdt))
         border = _chol_apply(chol, one.squeeze(-1).to(fdt)).to(dtype)
         border_sum = border.sum(1)
@@ -358,7 +359,7 @@ def solve_ipm(
         # tighter than the arithmetic allows) is not taken: that instance stops where it is.
         cand = (f + ap[:, None] * df, v + ap[:, None] * dv, t + ap * dt, s + ap[:, None] * ds,
                 y + ad[:, None] * dy, z + ad[:, None] * dz, q + ad[:, None] * dq)
-        finite = torch.ones(nb, dtype=torch.bool)
+        finite = torch.ones(nb, dtype=torch.bool, device=dev)
         for c in cand:
             finite &= torch.isfinite(c.reshape(nb, -1)).all(1)
         stopped = stopped | (~done & ~finite)

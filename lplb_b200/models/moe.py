@@ -52,7 +52,12 @@ class MoELayer:
         capacity_factor: float = 2.0,
         seed: int = 0,
         weight_scale: float | None = None,
+        capacity_rows: int | None = None,
     ) -> None:
+        """``capacity_rows`` sets the receive buffer's size in rows directly (rounded up to a
+        multiple of 128) instead of deriving it from ``max_tokens * topk * capacity_factor``.
+        Pairs that would land beyond it are dropped by their senders, contribute nothing to
+        the output and are reported (``check()`` returns the overflow code)."""
         from .. import _native
 
         if planner.device.type != "cuda":
@@ -77,7 +82,8 @@ class MoELayer:
         # a single GPU receives exactly its own pairs; with peers the LP bounds the imbalance,
         # and `capacity_factor` leaves room for it
         pairs = max_tokens * topk
-        capacity = int(-(-int(pairs * (capacity_factor if group is not None else 1.0)) // 128) * 128)
+        wanted = capacity_rows if capacity_rows is not None else int(pairs * (capacity_factor if group is not None else 1.0))
+        capacity = int(-(-max(1, int(wanted)) // 128) * 128)
         self.capacity = capacity
         self.engine = native.MoeEngine(
             hidden, inter, self.n_local, self.n_ranks, self.rank, topk, max_tokens, capacity, self.device.index
@@ -156,8 +162,11 @@ class MoELayer:
         return self.forward_physical(x, self.route(logical_idx, avail_counter, policy), weights)
 
     def check(self) -> int:
-        """First error code raised by the layer's kernels (0 = none); synchronises."""
-        return int(self.engine.status()[0])
+        """First error code raised by the layer's kernels (0 = none); synchronises.  In the
+        bounds-checking build an index that left its array is reported as code 6 (the access
+        was skipped; ``engine.status()[16:28]`` holds the record)."""
+        status = self.engine.status().tolist()
+        return int(status[0] or status[16])
 
     def reset(self) -> None:
         """Re-align the ranks after a timeout: clear every flag, counter and the status block

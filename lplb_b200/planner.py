@@ -35,6 +35,7 @@ import torch
 from . import lp as _lp
 from .mapping import ExpertMapping, build_mapping
 from .ops import reference as _ref
+from .parallel.exchange import PeerExchangeUnavailable
 from .topology import invert_r2o, validate_r2o
 
 log = logging.getLogger("lplb_b200")
@@ -50,6 +51,7 @@ _ERR_NAMES = {
     3: "lp_timeout",
     4: "bad_index",
     5: "lp_not_converged",
+    6: "index_out_of_bounds",
 }
 _PHASE_NAMES = {0: "-", 1: "count", 2: "exchange", 3: "solve", 4: "redirect"}
 
@@ -79,10 +81,11 @@ class Planner:
         peer_timeout_us: float = 1e6,
         grid_timeout_us: float = 1e6,
         allow_self_edges: bool = False,
-        warm_start: bool = False,
+        warm_start: bool = True,
         warm_guard: float = 0.1,
         warm_snap_mu: float = 1e-3,
         exchange_node_size: int = 0,
+        solver: str = "auto",
     ) -> None:
         """
         :param redundant_to_original: ``[group_size, num_redundants]``; rank ``i``'s
@@ -108,11 +111,18 @@ class Planner:
             residual at most ``warm_guard`` mean rank loads); typically one or two iterations
             instead of three to five when consecutive batches come from one distribution.
             Shares then depend on the planner's history, not only on the current batch; every
-            rank keeps its own (normally identical) state.  ``update_redundancy_mapping`` and
-            ``reset_exchange`` discard the state.
+            rank keeps its own (normally identical) state.  ``update_redundancy_mapping``,
+            ``reset_exchange`` and a step whose statistics exchange timed out discard the state
+            (that step and the next one solve cold).  On by default; ``False`` solves every batch
+            from scratch.
         :param exchange_node_size: run the in-kernel statistics exchange in two levels, inside
             nodes of this many consecutive ranks and then between nodes (the schedule for a
             topology that spans nodes, e.g. ``torus(2, 4)`` with 4); 0 = one all-to-all level.
+        :param solver: device LP solver: ``"warp"`` keeps a group of up to 32 ranks (4 replicas
+            per rank) in one warp's registers, ``"block"`` solves a group of up to 128 ranks
+            (8 replicas per rank) with one thread block and the matrix in shared memory,
+            ``"auto"`` uses the warp solver up to 8 ranks and the block solver above.  Larger
+            groups run the same method as tensor ops on the planner's device.
         """
         if device is None:
             device = "cuda" if torch.cuda.is_available() else "cpu"
@@ -158,6 +168,7 @@ class Planner:
         self._anchor: dict | None = None  # CPU path only; the engine keeps its own on the device
         self.exchange_node_size = int(exchange_node_size)
         self._host_out: tuple | None = None
+        self._status_mirror: list | None = None
         self._nvtx_on = self.device.type == "cuda" and os.environ.get("LPLB_B200_NVTX") == "1"
 
         self._engine = None
@@ -174,10 +185,15 @@ class Planner:
                 self.combined_redundant_experts,
                 self.device.index,
             )
+            if solver != "auto":
+                self._engine.set_solver(solver)
+            if os.environ.get("LPLB_B200_LEADER"):
+                self._engine.set_leader_mode(1 if os.environ["LPLB_B200_LEADER"] == "cta0" else 0)
             self._native_solver = bool(self._engine.has_native_solver())
             if not self._native_solver:
                 log.warning(
-                    "group of %d ranks x %d replicas exceeds the warp solver; the LP runs as tensor ops (slow path)",
+                    "group of %d ranks x %d replicas exceeds the device solvers; the LP runs as tensor ops "
+                    "with host synchronisation (slow path)",
                     self.group_size, self.num_redundants,
                 )
             self._engine.set_topology(self.r2o, self.o2r)
@@ -194,9 +210,11 @@ class Planner:
         if group is not None and comm != "none" and group.size() > 1:
             self.comm = "nccl"
             if comm in ("auto", "p2p") and self._engine is not None:
+                # init_peer_exchange fails on every rank of the group or on none, so all ranks
+                # take the same branch here and nobody mixes transports with its peers
                 try:
                     self.init_peer_exchange()
-                except Exception as exc:
+                except PeerExchangeUnavailable as exc:
                     if comm == "p2p":
                         raise
                     log.warning("peer-memory exchange unavailable (%s); using torch.distributed.all_reduce", exc)
@@ -206,8 +224,9 @@ class Planner:
         """Bring up the in-kernel NVLink statistics exchange (collective over the group).
 
         Allocates this rank's receive buffers, all-gathers CUDA-IPC handles through
-        ``torch.distributed`` and maps every peer.  Fails if a rank of the group lives
-        on another host.  Counterpart of the reference's ``init_comm``
+        ``torch.distributed`` and maps every peer.  Raises ``PeerExchangeUnavailable`` on
+        every rank if any rank cannot take part (a rank on another host, an allocation or a
+        mapping that failed).  Counterpart of the reference's ``init_comm``
         (reference ``csrc/plugin.cpp:357-456``), minus NVSHMEM.
         """
         from .parallel.exchange import open_peer_exchange
@@ -216,10 +235,10 @@ class Planner:
             return
         if self._engine is None or self.ep_group is None:
             raise RuntimeError("peer exchange needs a CUDA device and a process group")
+        if self.exchange_node_size and self.ep_group.size() % self.exchange_node_size:
+            raise ValueError("exchange_node_size must divide the number of ranks")
         open_peer_exchange(self._engine, self.ep_group, self.device)
         if self.exchange_node_size:
-            if self.ep_group.size() % self.exchange_node_size:
-                raise ValueError("exchange_node_size must divide the number of ranks")
             self._engine.set_exchange_nodes(self.exchange_node_size)
         self.deep_ep_initialized = True
         self.comm = "p2p"
@@ -318,16 +337,22 @@ class Planner:
             if self._native_solver:
                 probs, normalised = self._engine.solve(wl, avail_counter)
                 return probs, normalised.view(shape)
-            # groups larger than the warp solver's 32 ranks (or more than 4 replicas per rank):
-            # the same interior-point method as batched tensor ops on the device
+            # Groups beyond the device solvers (more than 128 ranks or 8 replicas per rank): the
+            # same interior-point method as batched tensor ops on the planner's device.  Nothing
+            # is copied to the host, but the iteration's loop control reads device flags, so this
+            # path synchronises the host several times per call.
             w, fixed = _lp.bundle_loads(
                 wl.double(), self.phy2log, self.n_group, self.group_size, self.num_redundants,
                 self.n_local_logical_routed_experts, self.combined_redundant_experts,
             )
-            res = _lp.solve_ipm(w.cpu(), fixed.cpu(), self.r2o.cpu(), max_iters=self.max_iters, tol=self.tol)
-            avail_counter += int(res.converged.sum())
+            res = _lp.solve_ipm(
+                w, fixed, self.r2o, max_iters=self.max_iters, tol=self.tol, warm_start=self.warm_start,
+                anchor=self._anchor, guard=self.warm_guard, snap_mu=self.warm_snap_mu,
+            )
+            self._anchor = res.anchor
+            avail_counter += res.converged.sum().to(avail_counter.dtype)
             peak = wl.max().clamp_min(1).float()
-            return res.f.float().to(self.device), (wl.float() / peak).view(shape)
+            return res.f.float(), (wl.float() / peak).view(shape)
 
         wl = workload.reshape(-1).to(torch.int64)
         if self.comm == "nccl":
@@ -419,11 +444,8 @@ class Planner:
         return None if self._engine is None else self._engine.last_probs()
 
     # ------------------------------------------------------------------ observability
-    def check_status(self, clear: bool = False) -> PlannerStatus:
-        """Read the engine's status block (one small device-to-host copy)."""
-        if self._engine is None:
-            return PlannerStatus(error="ok", phase="-", detail=0, calls=0, lp_iters=0, lp_failures=0, timeouts=0, bad_indices=0)
-        raw = self._engine.status().cpu().tolist()
+    @staticmethod
+    def _decode_status(raw: list[int]) -> PlannerStatus:
         out = PlannerStatus(
             error=_ERR_NAMES.get(raw[0], str(raw[0])),
             phase=_PHASE_NAMES.get(raw[1], str(raw[1])),
@@ -433,10 +455,50 @@ class Planner:
             lp_failures=raw[5],
             timeouts=raw[6],
             bad_indices=raw[7],
+            lp_gap=raw[8] * 1e-9,
         )
+        if raw[0] == 6 or raw[11]:
+            out.update(bounds_line=raw[2], bounds_index=raw[9], bounds_limit=raw[10], bounds_skipped=raw[11])
+        return out
+
+    def check_status(self, clear: bool = False) -> PlannerStatus:
+        """Read the engine's status block (one small blocking device-to-host copy).
+
+        ``lp_gap`` is the largest relative duality gap among the groups of the last launch,
+        ``lp_iters`` the iterations of its slowest group; the other counters are cumulative."""
+        if self._engine is None:
+            return PlannerStatus(error="ok", phase="-", detail=0, calls=0, lp_iters=0, lp_failures=0, timeouts=0,
+                                 bad_indices=0, lp_gap=0.0)
+        out = self._decode_status(self._engine.status().cpu().tolist())
         if clear:
             self._engine.status().zero_()
         return out
+
+    def poll_status(self) -> PlannerStatus | None:
+        """Status without stalling the host: every call enqueues a copy of the status block into
+        pinned host memory on the current stream and returns the decoded result of the most
+        recent copy that has *completed* (``None`` until the first one has).  Meant to be
+        called once per step from a training loop: the answer lags the device by a step or
+        so and costs no synchronisation."""
+        if self._engine is None:
+            return self.check_status()
+        if self._status_mirror is None:
+            self._status_mirror = [
+                (torch.empty(16, dtype=torch.int32).pin_memory(), torch.cuda.Event()) for _ in range(2)
+            ]
+            self._status_pending: list[int] = []
+            self._status_last: PlannerStatus | None = None
+        # newest completed copy wins; keep at most two in flight
+        while self._status_pending and self._status_mirror[self._status_pending[0]][1].query():
+            slot = self._status_pending.pop(0)
+            self._status_last = self._decode_status(self._status_mirror[slot][0].tolist())
+        if len(self._status_pending) < 2:
+            slot = next(i for i in range(2) if i not in self._status_pending)
+            buf, event = self._status_mirror[slot]
+            buf.copy_(self._engine.status(), non_blocking=True)
+            event.record()
+            self._status_pending.append(slot)
+        return self._status_last
 
     def _nvtx(self, name: str):
         """NVTX range around the hot path when LPLB_B200_NVTX=1 (for timeline profilers)."""
@@ -471,13 +533,34 @@ class Planner:
             self._engine.enable_trace(bool(on))
 
     def phase_times_us(self) -> dict[str, float] | None:
-        """Phase durations of the last fused ``run`` in microseconds; synchronises."""
+        """Phase durations of the last fused ``run`` in microseconds; synchronises.
+
+        ``count`` and ``redirect`` are CTA 0's; ``last_count`` is the wait until the last CTA's
+        counts were in; ``exchange``, ``solve`` belong to the CTA that took the last arrival
+        ticket.  With a peer exchange the ``exchange`` phase is split further, measured from its
+        start: ``xchg_pushed`` (this rank's stores to all peers issued), ``xchg_first_peer`` and
+        ``xchg_last_peer`` (first and last word of another rank seen), and ``xchg_last_peer_rank``;
+        what lies between ``xchg_pushed`` and ``xchg_last_peer`` is wire time plus waiting for the
+        slowest rank.  A two-level exchange reports its second level as ``xchg2_*``."""
         if self._engine is None or self._engine.trace() is None:
             return None
         t = self._engine.trace().cpu().tolist()
-        names = ["count", "grid_barrier", "exchange", "solve", "redirect", "drain"]
-        out = {n: (t[i + 1] - t[i]) / 1e3 for i, n in enumerate(names)}
-        out["total"] = (t[6] - t[0]) / 1e3
+        out = {
+            "count": (t[1] - t[0]) / 1e3,
+            "last_count": (t[2] - t[1]) / 1e3,
+            "exchange": (t[3] - t[2]) / 1e3,
+            "solve": (t[4] - t[3]) / 1e3,
+            "redirect": (t[5] - t[4]) / 1e3,
+            "drain": (t[6] - t[5]) / 1e3,
+            "total": (t[6] - t[0]) / 1e3,
+        }
+        if self.comm == "p2p":
+            for base, tag in ((8, "xchg"), (12, "xchg2")):
+                if t[base] and t[base] >= t[2]:
+                    out[f"{tag}_pushed"] = (t[base] - t[2]) / 1e3
+                    out[f"{tag}_first_peer"] = (t[base + 1] - t[2]) / 1e3
+                    out[f"{tag}_last_peer"] = (t[base + 2] - t[2]) / 1e3
+                    out[f"{tag}_last_peer_rank"] = int(t[base + 3])
         return out
 
     # ------------------------------------------------------------------ checkpointing

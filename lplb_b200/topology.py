@@ -18,6 +18,7 @@ import torch
 
 __all__ = [
     "ring",
+    "circulant",
     "cube",
     "hypercube",
     "torus",
@@ -43,6 +44,19 @@ def ring(n: int = 8) -> torch.Tensor:
     if n < 2:
         raise ValueError("a ring needs at least 2 ranks")
     return _as_tensor([[(i + 1) % n for i in range(n)]])
+
+
+def circulant(n: int, shifts: Sequence[int] = (1,)) -> torch.Tensor:
+    """``len(shifts)`` redundant slots per rank: slot ``d`` copies from the rank ``shifts[d]``
+    places further around a ring of ``n`` ranks.  ``circulant(n, (1,))`` is ``ring(n)``; more
+    shifts give denser graphs for any number of ranks and replicas (the reference has no
+    generator for those; its shapes are the literals of reference ``tests/utils.py:97-119``).
+    """
+    if n < 2 or not shifts:
+        raise ValueError("a circulant topology needs at least 2 ranks and 1 shift")
+    if any(s % n == 0 for s in shifts):
+        raise ValueError("a shift that is a multiple of the rank count is a self edge")
+    return _as_tensor([[(i + s) % n for i in range(n)] for s in shifts])
 
 
 def _quad_shift(n: int) -> list[int]:

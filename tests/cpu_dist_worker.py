@@ -12,10 +12,57 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 from lplb_b200 import Planner, cube  # noqa: E402
 
 
+class FakeEngine:
+    """Stands in for the native engine's exchange calls; `fail_in` makes one of them raise."""
+
+    def __init__(self, fail_in=None):
+        self.fail_in, self.opened, self.closed = fail_in, None, 0
+
+    def alloc_exchange(self, world, rank):
+        if self.fail_in == "alloc":
+            raise MemoryError("no memory for the receive buffers")
+        return bytes([rank]) * 64
+
+    def open_exchange(self, handles):
+        if self.fail_in == "open":
+            raise RuntimeError("peer handle cannot be mapped")
+        self.opened = list(handles)
+
+    def close_exchange(self):
+        self.closed += 1
+
+
+def check_bootstrap_outcome_is_collective(rank, world):
+    """One rank fails locally (environment switch, allocation, mapping): every rank must get
+    PeerExchangeUnavailable naming that rank, nobody hangs, nobody keeps buffers; with no
+    failure every rank ends with all handles."""
+    from lplb_b200.parallel.exchange import PeerExchangeUnavailable, open_peer_exchange
+
+    cpu = torch.device("cpu")
+    group = dist.group.WORLD
+    for failing_rank, how in ((1, "env"), (0, "alloc"), (1, "open")):
+        engine = FakeEngine(fail_in=how if rank == failing_rank and how != "env" else None)
+        if how == "env" and rank == failing_rank:
+            os.environ["LPLB_B200_DISABLE_P2P"] = "1"
+        try:
+            open_peer_exchange(engine, group, cpu)
+        except PeerExchangeUnavailable as exc:
+            assert list(exc.reasons) == [failing_rank], exc.reasons
+            assert engine.closed == 1
+        else:
+            raise AssertionError(f"rank {rank}: bootstrap succeeded although rank {failing_rank} failed ({how})")
+        finally:
+            os.environ.pop("LPLB_B200_DISABLE_P2P", None)
+    engine = FakeEngine()
+    open_peer_exchange(engine, group, cpu)
+    assert engine.opened == [bytes([r]) * 64 for r in range(world)] and engine.closed == 0
+
+
 def main():
     dist.init_process_group("gloo")
     rank, world = dist.get_rank(), dist.get_world_size()
-    planner = Planner(cube(), 64 + 16, 64, 8, dist.group.WORLD, device="cpu", comm="auto")
+    # cold solves: the shares are compared with a fresh single-process planner below
+    planner = Planner(cube(), 64 + 16, 64, 8, dist.group.WORLD, device="cpu", comm="auto", warm_start=False)
     assert planner.comm == "nccl"  # no peer memory on a CPU device: torch.distributed carries the statistics
     g = torch.Generator().manual_seed(100 + rank)
     history = torch.randint(100, 1000, (64,), generator=torch.Generator().manual_seed(1))
@@ -37,6 +84,7 @@ def main():
         assert torch.allclose(want, probs, atol=1e-6)
         out = planner.run(idx, avail, 4)
         assert out.shape == idx.shape and bool(((out == -1) == (idx == -1)).all())
+    check_bootstrap_outcome_is_collective(rank, world)
     dist.barrier()
     if rank == 0:
         print("CPU_DIST_OK", world)

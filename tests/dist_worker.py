@@ -24,7 +24,8 @@ def main():
     dist.init_process_group("nccl", device_id=dev)
     group = dist.group.WORLD
 
-    planner = Planner(cube(), 256 + 16, 256, 8, group, device=dev, comm="p2p", peer_timeout_us=2e5)
+    # cold solves here: the steps below compare shares bit for bit with a second planner
+    planner = Planner(cube(), 256 + 16, 256, 8, group, device=dev, comm="p2p", peer_timeout_us=2e5, warm_start=False)
     assert planner.comm == "p2p" and planner.deep_ep_initialized
 
     # 1. stand-alone exchange is bitwise equal to NCCL's all-reduce, many times in a row
@@ -64,6 +65,30 @@ def main():
         assert planner.check_status().ok
     hist = counts
 
+    # 2a. four LP groups (ep_size 32 on the Cube) and four redundant experts per rank (two per
+    # topology slot), statistics from the `world` real ranks over the in-kernel exchange
+    keep_alive = []
+    for name, ep_size, n_red in (("four groups", 32, 2), ("two experts per slot", 8, 4)):
+        multi = Planner(cube(), 256 + n_red * ep_size, 256, ep_size, group, device=dev, comm="p2p", warm_start=False)
+        for step in range(4):
+            logits = torch.randn(2048, 256, device=dev, generator=gen) + bias
+            idx = logits.bfloat16().topk(8, dim=-1).indices
+            counts = torch.bincount(idx.reshape(-1), minlength=256)
+            dist.all_reduce(counts, group=group)
+            if step == 1:
+                multi.update_redundancy_mapping(counts)
+            avail = torch.zeros(1, dtype=torch.int32, device=dev)
+            multi.run(idx, avail, 148 if step % 2 else 20)
+            assert int(avail) == multi.n_group, name
+            ws = multi._engine.workspace()
+            assert torch.equal(ws[8 + 2 * 256 : 8 + 3 * 256].long(), counts), f"rank {rank}: {name}: global counts differ"
+            probs = multi.last_probs.clone()
+            gathered = [torch.empty_like(probs) for _ in range(world)]
+            dist.all_gather(gathered, probs, group=group)
+            assert all(torch.equal(g, probs) for g in gathered), f"{name}: shares differ between ranks"
+            assert multi.check_status().ok
+        keep_alive.append(multi)  # peers stay mapped until every rank is done
+
     # 3. a rank skips one step: the others' wait runs out, they report it and still route
     dist.barrier(group=group)
     torch.cuda.synchronize(dev)
@@ -90,7 +115,7 @@ def main():
         assert planner.check_status().ok
 
     # 4. the NCCL pipeline gives the same shares as the fused kernel
-    staged = Planner(cube(), 256 + 16, 256, 8, group, device=dev, comm="nccl")
+    staged = Planner(cube(), 256 + 16, 256, 8, group, device=dev, comm="nccl", warm_start=False)
     staged.load_state_dict(planner.state_dict())
     avail.zero_()
     out_f = planner.run(idx, avail)
@@ -100,7 +125,8 @@ def main():
 
     # 4a. two-level schedule (nodes of world/2 ranks) is bitwise equal to the all-reduce as well
     if world >= 4:
-        two = Planner(cube(), 256 + 16, 256, 8, group, device=dev, comm="p2p", exchange_node_size=world // 2)
+        two = Planner(cube(), 256 + 16, 256, 8, group, device=dev, comm="p2p", exchange_node_size=world // 2,
+                      warm_start=False)
         for step in range(10):
             mine = torch.randint(0, 5000, (256,), device=dev, generator=gen, dtype=torch.int32)
             want = mine.clone()
@@ -115,7 +141,8 @@ def main():
         assert two.check_status().ok
 
     # 4b. warm-started solves stay identical on every rank (same history, same arithmetic)
-    warm = Planner(cube(), 256 + 16, 256, 8, group, device=dev, comm="p2p", warm_start=True)
+    warm = Planner(cube(), 256 + 16, 256, 8, group, device=dev, comm="p2p", peer_timeout_us=2e5)
+    assert warm.warm_start  # the library default
     warm.load_state_dict(planner.state_dict())
     warm_iters = []
     for step in range(6):
@@ -131,6 +158,29 @@ def main():
         assert st.ok and int(avail) == 1
         warm_iters.append(st["lp_iters"])
     assert min(warm_iters[1:]) < warm_iters[0], warm_iters
+    # 4c. a step whose exchange times out must not leave a saved iterate behind: the ranks that
+    # saw the timeout drop theirs inside the kernel, and after the collective reset every rank
+    # starts cold again, so the shares agree without anybody having to remember to invalidate
+    dist.barrier(group=group)
+    torch.cuda.synchronize(dev)
+    idx = (torch.randn(1024, 256, device=dev, generator=gen) + bias).topk(8, dim=-1).indices
+    if rank != world - 1:
+        avail.zero_()
+        warm.run(idx, avail)
+        torch.cuda.synchronize(dev)
+        st = warm.check_status(clear=True)
+        assert st["error"] == "peer_timeout", st
+        assert int(warm._engine.warm_start_valid().sum()) == 0, "a timed-out step left a warm-start state behind"
+    warm.reset_exchange()
+    for step in range(3):
+        idx = (torch.randn(4096, 256, device=dev, generator=gen) + bias).bfloat16().topk(8, dim=-1).indices
+        avail.zero_()
+        warm.run(idx, avail)
+        probs = warm.last_probs.clone()
+        gathered = [torch.empty_like(probs) for _ in range(world)]
+        dist.all_gather(gathered, probs, group=group)
+        assert all(torch.equal(g, probs) for g in gathered), "shares differ between ranks after a timeout and a reset"
+        assert warm.check_status(clear=True).ok
 
     # 5. expert-parallel MoE layer over the same ranks: dispatch and combine cross NVLink
     from lplb_b200 import ring
@@ -139,7 +189,7 @@ def main():
     r2o = cube() if world == 8 else ring(world)
     red = r2o.shape[1]
     n_logical = 4 * world
-    mp = Planner(r2o, n_logical + red * world, n_logical, world, group, device=dev, comm="p2p")
+    mp = Planner(r2o, n_logical + red * world, n_logical, world, group, device=dev, comm="p2p", warm_start=False)
     layer = MoELayer(mp, 512, 256, 4, max_tokens=512, group=group, capacity_factor=4.0)
     layer.engine.set_timeout_us(2e5)
     single = Planner(r2o, n_logical + red * world, n_logical, world, device=dev)  # reference weights only

@@ -11,7 +11,7 @@ pytestmark = pytest.mark.gpu
 
 def _layer(hidden, inter, n_logical, topk, max_tokens, r2o=None, red=2):
     r2o = cube() if r2o is None else r2o
-    planner = Planner(r2o, n_logical + red * 8, n_logical, 8, device="cuda")
+    planner = Planner(r2o, n_logical + red * 8, n_logical, 8, device="cuda", warm_start=False)
     layer = MoELayer(planner, hidden, inter, topk, max_tokens=max_tokens)
     layer.engine.set_timeout_us(1e5)  # a mis-programmed pipeline ends in 0.1 s, with an error code
     return planner, layer
@@ -137,16 +137,95 @@ def test_reset_restarts_the_launch_numbering_and_the_layer_keeps_working():
     assert layer.check() == 0 and int(layer.engine.epoch()) == 3
 
 
-def test_receive_buffer_overflow_is_reported_not_written():
-    planner = Planner(cube(), 32 + 16, 32, 8, device="cuda")
-    layer = MoELayer(planner, 256, 128, 4, max_tokens=128)  # capacity 512 rows
+MOE_OVERFLOW = 13  # kMoeOverflow in csrc/moe_gemm.cuh
+
+
+def _per_row_error(out, ref):
+    """Largest error of a row relative to that row's norm: a wrong tile on a row with few or
+    small contributions shows up here even when the tensor-wide maximum hides it."""
+    num = (out.float() - ref.float()).norm(dim=1)
+    den = ref.float().norm(dim=1).clamp_min(1e-3 * float(ref.float().norm(dim=1).mean()))
+    return float((num / den).max())
+
+
+@pytest.mark.parametrize("mode", ["unfused", "fused-warps", "fused-ctas"])
+def test_layer_at_the_benchmark_shape_row_by_row(mode):
+    """hidden 7168, SwiGLU 2048: 112 K-blocks in the first GEMM and 32 in the second, 16 and 56
+    N-tiles, so the pipeline stages and barrier phases wrap dozens of times per tile.  Four
+    logical experts (plus replicas) with a few hundred rows each; checked per row."""
+    r2o = ring(2)
+    planner = Planner(r2o, 4 + 2, 4, 2, device="cuda", warm_start=False)
+    layer = MoELayer(planner, 7168, 2048, 2, max_tokens=640, weight_scale=7168**-0.5)
+    layer.engine.set_timeout_us(2e5)
+    g = torch.Generator("cuda").manual_seed(5)
+    x = torch.randn(600, 7168, device="cuda", generator=g).bfloat16()
+    logits = torch.randn(600, 4, device="cuda", generator=g) + torch.tensor([1.0, 0.0, -1.0, 0.5], device="cuda")
+    w, idx = torch.softmax(logits, -1).topk(2, dim=-1)
+    idx[::17, 1] = -1  # some tokens use one expert only
+    planner.update_redundancy_mapping(torch.bincount(idx[idx >= 0].reshape(-1), minlength=4))
+    layer.place_weights()
+    layer.fuse_dispatch = mode != "unfused"
+    layer.send_ctas = 16 if mode == "fused-ctas" else 0
+    avail = torch.zeros(1, dtype=torch.int32, device="cuda")
+    ref = layer.reference_forward(x, idx, w)
+    for policy in ("lplb", "static"):
+        out = layer.forward(x, idx, w, avail, policy)
+        torch.cuda.synchronize()
+        assert layer.check() == 0, layer.engine.status().tolist()
+        assert _per_row_error(out, ref) < 1e-2, (mode, policy)
+    # the first GEMM's rows on their own (SwiGLU epilogue), per row as well
+    phys = layer.route(idx, avail, "lplb")
+    layer.forward_physical(x, phys, w, upto=3)
+    torch.cuda.synchronize()
+    plan, nl = layer.engine.plan().cpu(), layer.n_local
+    for slot in range(nl):
+        n, s0 = int(plan[slot]), int(plan[nl + slot])
+        if n == 0:
+            continue
+        gate, up, _ = layer.logical_weights(int(planner.phy2log[slot]))
+        xin = layer.engine.recv_x()[s0 : s0 + n].float()
+        want = torch.nn.functional.silu(xin @ gate.float().T) * (xin @ up.float().T)
+        assert _per_row_error(layer.engine.act()[s0 : s0 + n], want) < 1e-2, (mode, slot)
+
+
+@pytest.mark.parametrize("fused", [False, True])
+def test_receive_buffer_overflow_drops_pairs_and_reports(fused):
+    """A receive buffer smaller than the routed pairs: the senders drop what does not fit, the
+    status block says so, the kept pairs give exactly what they give without the overflow,
+    the dropped ones contribute nothing, and nothing is written past the buffer."""
+    planner = Planner(cube(), 32 + 16, 32, 8, device="cuda", warm_start=False)
+    layer = MoELayer(planner, 256, 128, 4, max_tokens=256, capacity_rows=384)  # 1024 pairs arrive
+    assert layer.capacity == 384
     layer.engine.set_timeout_us(1e5)
-    x, idx, w = _inputs(128, 256, 32, 4)
+    layer.fuse_dispatch = fused
+    with pytest.raises(RuntimeError):  # more tokens than the layer was built for: refused on the host
+        big = _inputs(257, 256, 32, 4)
+        layer.forward_physical(big[0], big[1], big[2])
+    x, idx, w = _inputs(256, 256, 32, 4)
     phys = layer.route(idx, torch.zeros(1, dtype=torch.int32, device="cuda"), "static")
-    # pretend the layer was sized for fewer tokens than it gets: shrink by dropping nothing,
-    # instead overfill with a second engine call of 256 tokens is refused on the host
-    with pytest.raises(RuntimeError):
-        layer.forward_physical(torch.cat([x, x]), torch.cat([phys, phys]), torch.cat([w, w]))
     out = layer.forward_physical(x, phys, w)
     torch.cuda.synchronize()
-    assert layer.check() == 0 and bool(torch.isfinite(out.float()).all())
+    assert layer.check() == MOE_OVERFLOW
+    slots = layer.engine.pair_slot()[: phys.numel()].reshape(phys.shape)
+    kept = slots >= 0
+    assert int(kept.sum()) == 384  # exactly the capacity was used, the rest dropped
+    rows = layer.engine.plan()[: layer.n_local].long()
+    assert int(rows.sum()) == 384
+    meta = layer.engine.recv_meta()[:384].long()
+    assert sorted((meta & 0xFFFFF).tolist()) == sorted(slots[kept].tolist())  # every kept row has its return slot
+    assert bool(torch.isfinite(out.float()).all())
+    ref = layer.reference_forward(x, torch.where(kept, idx, torch.full_like(idx, -1)), w)
+    scale = float(ref.float().abs().max())
+    assert float((out.float() - ref.float()).abs().max()) < 2e-2 * scale
+    untouched = ~kept.any(dim=1)  # tokens that lost every pair come back as zeros
+    if bool(untouched.any()):
+        assert float(out[untouched].float().abs().max()) == 0.0
+    # the layer recovers once the status is cleared and the batch fits
+    layer.reset()
+    small = _inputs(64, 256, 32, 4, seed=3)
+    phys = layer.route(small[1], torch.zeros(1, dtype=torch.int32, device="cuda"), "static")
+    out = layer.forward_physical(small[0], phys, small[2])
+    torch.cuda.synchronize()
+    assert layer.check() == 0
+    ref = layer.reference_forward(*small).float()
+    assert float((out.float() - ref).abs().max() / ref.abs().max()) < 2e-2

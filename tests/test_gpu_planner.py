@@ -15,6 +15,9 @@ pytestmark = pytest.mark.gpu
 
 
 def _planner(r2o, n_logical, ep_size, n_red, **kw):
+    # most tests below compare launches bit for bit, so they solve every batch from scratch;
+    # the warm-start default of the library has tests of its own
+    kw.setdefault("warm_start", False)
     return Planner(r2o, n_logical + n_red * ep_size, n_logical, ep_size, device="cuda", **kw)
 
 
@@ -392,24 +395,136 @@ def test_exchange_loopback_sums_prefilled_peer():
     _check_redirect(planner, idx, out, eng.last_probs())
 
 
-def test_groups_beyond_the_warp_solver_take_the_tensor_op_path():
-    # torus(8, 8): one LP group of 64 ranks.  Counting and redirect stay native, the LP runs as
-    # batched tensor ops; the public API is unchanged.
+def test_groups_beyond_a_warp_run_the_fused_single_launch_without_a_host_sync():
+    # torus(8, 8): one LP group of 64 ranks, solved by the thread-block solver inside the fused
+    # kernel; the whole step is one launch and the host never waits for the device
     planner = _planner(topology.torus(8, 8), 512, 64, 2)
-    assert planner._native_solver is False
+    assert planner._native_solver is True and planner._engine.solver() == "block"
     gen = torch.Generator("cuda").manual_seed(2)
     idx = (torch.randn(4096, 512, device="cuda", generator=gen) + torch.randn(512, device="cuda", generator=gen)).topk(8, dim=-1).indices
     planner.update_redundancy_mapping(torch.bincount(idx.reshape(-1), minlength=512))
     avail = torch.zeros(1, dtype=torch.int32, device="cuda")
-    counts, by_sm = planner.count_workload(idx, _sms())
-    probs, _ = planner.solve_probs(counts, avail)
-    assert int(avail) == 1 and probs.shape == (1, 64, 2)
-    out = planner.run(idx, avail)
+    planner.run(idx, avail)  # first call: attribute and occupancy queries
+    calls = planner.check_status()["calls"]
+    torch.cuda.synchronize()
+    torch.cuda.set_sync_debug_mode("error")  # any host synchronisation raises from here on
+    try:
+        out = planner.run(idx, avail)
+    finally:
+        torch.cuda.set_sync_debug_mode("default")
+    probs = planner.last_probs.clone()
+    assert int(avail) == 2 and probs.shape == (1, 64, 2)
+    assert planner.check_status()["calls"] == calls + 1
     _check_redirect(planner, idx, out, probs)
+    counts, _ = planner.count_workload(idx, _sms())
     w, fixed = lp.bundle_loads(counts.cpu().double(), planner.phy2log.cpu(), 1, 64, 2, 8, 1)
     realised = float(lp.rank_loads(probs.cpu().double(), w, fixed, topology.torus(8, 8)).max())
     _, t_opt = lp.solve_highs(w[0], fixed[0], topology.torus(8, 8))
     assert (realised - t_opt) / t_opt < 1e-3
+    st = planner.check_status()
+    assert st.ok and 0 <= st["lp_gap"] <= 1e-4 and st["lp_iters"] <= 12
+
+
+@pytest.mark.parametrize("name,r2o,ll", [
+    ("cube", topology.cube(), 8),
+    ("ring5", topology.ring(5), 4),
+    ("hypercube", topology.hypercube(), 8),
+    ("torus8x4", topology.torus(8, 4), 8),
+    ("ring100", topology.ring(100), 2),
+    ("circulant12x3", topology.circulant(12, (1, 2, 5)), 6),
+    ("circulant10x5", topology.circulant(10, (1, 2, 3, 4, 5)), 8),
+    ("circulant128x4", topology.circulant(128, (1, 2, 64, 127)), 8),
+])
+def test_block_solver_reaches_the_optimum_for_any_group_shape(name, r2o, ll):
+    """The thread-block solver on group sizes that are not multiples of 8 or 32, on every
+    instantiated replica count and on the padded one (5 replicas run as 8), warm and cold."""
+    g, d = r2o.shape
+    planner = _planner(r2o, g * ll, g, d, solver="block", warm_start=True)
+    assert planner._engine.solver() == "block"
+    gen = torch.Generator().manual_seed(11)
+    base = (torch.rand(g * ll, generator=gen) + 0.5) * 4000
+    iters = []
+    for step in range(3):
+        counts = (base * (1 + 0.03 * torch.randn(g * ll, generator=gen))).clamp_min(0).int().cuda()
+        avail = torch.zeros(1, dtype=torch.int32, device="cuda")
+        probs, _ = planner.solve_probs(counts, avail)
+        assert int(avail) == 1 and float(probs.min()) >= 0 and float(probs.max()) <= 1
+        w, fixed = lp.bundle_loads(counts.cpu().double(), planner.phy2log.cpu(), 1, g, d, ll, 1)
+        realised = float(lp.rank_loads(probs.cpu().double(), w, fixed, r2o).max())
+        _, t_opt = lp.solve_highs(w[0], fixed[0], r2o)
+        assert -1e-6 < (realised - t_opt) / t_opt < 1e-3, (name, step, realised, t_opt)
+        st = planner.check_status(clear=True)
+        assert st.ok and st["lp_gap"] <= 1e-4
+        iters.append(st["lp_iters"])
+    assert iters[1] <= iters[0] and iters[2] <= iters[0]  # later batches start from the saved iterate
+
+
+def test_block_and_warp_solver_agree():
+    gen = torch.Generator().manual_seed(4)
+    for r2o, ll, n_group in ((topology.cube(), 8, 3), (topology.hypercube(), 4, 2), (topology.torus(8, 4), 4, 1)):
+        g, d = r2o.shape
+        e = g * ll * n_group
+        warp = _planner(r2o, e, g * n_group, d, solver="warp")
+        block = _planner(r2o, e, g * n_group, d, solver="block")
+        assert (warp._engine.solver(), block._engine.solver()) == ("warp", "block")
+        counts = (torch.rand(e, generator=gen) * 5000).int().cuda()
+        a1 = torch.zeros(1, dtype=torch.int32, device="cuda")
+        a2 = torch.zeros(1, dtype=torch.int32, device="cuda")
+        p1, n1 = warp.solve_probs(counts, a1)
+        p2, n2 = block.solve_probs(counts, a2)
+        assert int(a1) == int(a2) == n_group and torch.equal(n1, n2)
+        assert float((p1 - p2).abs().max()) < 2e-4  # same method, different elimination order
+        assert warp.check_status()["lp_iters"] == block.check_status()["lp_iters"]
+        # and inside the fused kernel
+        idx = torch.randint(-1, e, (3000, 4), device="cuda")
+        o1, o2 = warp.run(idx, a1), block.run(idx, a2)
+        _check_redirect(block, idx, o2, block.last_probs.clone())
+        assert float((warp.last_probs - block.last_probs).abs().max()) < 2e-4
+
+
+def test_odd_number_of_experts_keeps_the_tables_aligned():
+    # 9 ranks x 3 logical experts = 27: the int2 table of the redirect phase must not depend on
+    # the parity of the expert count
+    r2o = topology.torus(3, 3)
+    planner = _planner(r2o, 27, 9, 2)
+    idx = torch.randint(-1, 27, (5000, 2), device="cuda", generator=torch.Generator("cuda").manual_seed(1))
+    avail = torch.zeros(1, dtype=torch.int32, device="cuda")
+    out = planner.run(idx, avail, 7)
+    assert int(avail) == 1
+    _check_redirect(planner, idx, out, planner.last_probs.clone())
+    counts, by_sm = planner.count_workload(idx, 5)
+    probs, _ = planner.solve_probs(counts, avail)
+    staged = planner.weighted_select_target(idx, probs, by_sm, 5)
+    _check_redirect(planner, idx, staged, probs)
+    # the exchange pushes single words instead of pairs when the count is odd
+    eng = planner._engine
+    eng.open_exchange_loopback(2, 0)
+    peer = torch.arange(27, dtype=torch.int32) * 7
+    eng.debug_fill_slot(1, peer, eng.completed_launches() + 1)
+    mine = torch.randint(0, 100, (27,), dtype=torch.int32, device="cuda")
+    assert torch.equal(eng.all_reduce_counts(mine).cpu(), mine.cpu() + peer)
+    assert planner.check_status().ok
+
+
+def test_library_default_is_warm_started_and_status_can_be_polled():
+    planner = Planner(topology.cube(), 272, 256, 8, device="cuda")
+    assert planner.warm_start is True
+    gen = torch.Generator("cuda").manual_seed(21)
+    bias = torch.randn(256, device="cuda", generator=gen)
+    avail = torch.zeros(1, dtype=torch.int32, device="cuda")
+    iters, seen = [], None
+    for step in range(4):
+        idx = (torch.randn(8192, 256, device="cuda", generator=gen) + bias).bfloat16().topk(8, dim=-1).indices
+        out = planner.run(idx, avail)
+        _check_redirect(planner, idx, out, planner.last_probs.clone())
+        polled = planner.poll_status()  # never blocks; lags by a call or two
+        seen = polled or seen
+        iters.append(planner.check_status()["lp_iters"])
+    assert min(iters[1:]) < iters[0], iters
+    torch.cuda.synchronize()
+    last = planner.poll_status()
+    assert last is not None and last.ok and last["calls"] >= 3
+    assert planner.check_status()["calls"] == 4
 
 
 def test_two_level_exchange_on_one_gpu():

@@ -74,3 +74,25 @@ def test_sizes_beyond_the_fixed_scratch_are_refused(entry):
     assert rc == 0, msg
     torch.cuda.synchronize()
     assert out[:MAX_EXPERTS].tolist()[:2] == [16, 0]
+
+
+def test_a_call_after_the_warm_up_leaves_device_memory_as_it_was(entry):
+    """The claim a caller with its own memory pool relies on: once the first call on the device
+    has run (it loads the library's device image, array included), later calls take no device
+    memory, neither from the driver nor from the framework's allocator."""
+    torch.cuda.set_device(0)
+    idx = torch.randint(-1, 256, (4096, 8), device="cuda")
+    out = torch.zeros(256, dtype=torch.int32, device="cuda")
+    rc, msg = _call(entry, idx, 256, 148, out)  # warm-up
+    assert rc == 0, msg
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info()
+    torch_before = torch.cuda.memory_allocated(), torch.cuda.memory_reserved()
+    for n_cta in (148, 7):
+        rc, msg = _call(entry, idx, 256, n_cta, out)
+        assert rc == 0, msg
+    torch.cuda.synchronize()
+    free_after, _ = torch.cuda.mem_get_info()
+    assert free_after == free_before
+    assert (torch.cuda.memory_allocated(), torch.cuda.memory_reserved()) == torch_before
+    assert int(out.sum()) == int((idx >= 0).sum())
