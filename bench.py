@@ -149,9 +149,12 @@ def run_ours(args) -> dict:
         """Run fn(position) for every timed step between CUDA events.  Steps are enqueued in
         chunks (one bias period at most) behind a ~10 ms device-side sleep, so the host is far
         ahead of the GPU and host scheduling jitter cannot open gaps inside an event pair.  On
-        several GPUs every timed step is preceded, outside its event pair, by one stand-alone
-        statistics exchange: the ranks leave it within an NVLink round trip of each other, so a
-        step is not charged for the time by which the L2 flush of another GPU ran longer."""
+        several GPUs one untimed stand-alone statistics exchange runs before every L2 flush: the
+        ranks leave it within an NVLink round trip of each other, so a step is charged for the
+        skew of one flush, not for whatever the ranks have drifted apart since the sleep.  (It
+        must come before the flush, not after it: a small kernel between the flush and the timed
+        launch displaces the solver's code from CTA 0's instruction cache, and the solve then
+        runs twice as long.)"""
         starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
         ends = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
         align = who.comm == "p2p"
@@ -164,9 +167,9 @@ def run_ours(args) -> dict:
             barrier()
             torch.cuda._sleep(sleep_cycles)
             for j in range(k, k + n):
-                flush.fill_(j & 0xFF)  # evict L2 between timed iterations
                 if align:
                     who._engine.all_reduce_counts(align_src)
+                flush.fill_(j & 0xFF)  # evict L2 between timed iterations
                 starts[j].record()
                 fn(args.warmup + j)
                 ends[j].record()
@@ -331,8 +334,8 @@ def run_ours(args) -> dict:
             "slow_path": "update_redundancy_mapping runs at every bias redraw (every 50 steps, one of them inside "
                          "the timed steps), between timed chunks; the cold solves after it are timed",
             "launch": "timed steps are enqueued behind a 12 ms device sleep so host jitter stays outside the event "
-                      "pairs; on several GPUs one untimed stand-alone statistics exchange before every start event "
-                      "re-aligns the ranks after the L2 flush",
+                      "pairs; on several GPUs one untimed stand-alone statistics exchange before every L2 flush "
+                      "re-aligns the ranks",
         },
         "clocks": clocks.summary(),
         "e2e": {

@@ -87,16 +87,20 @@ def main():
         return t
 
     clocks = {}
+    max_rows = {}
 
     def run_policy(policy, upto=5):
-        """Per-step device ms (max over ranks, mean over steps) and the max/mean rank load."""
+        """Per-step device ms (max over ranks, mean over steps) and the max/mean rank load.
+        SM clock, board power and throttle reasons are sampled on every rank while it runs."""
         with ClockSampler(physical_gpu_index(local), period_s=0.002) as sampler:
             out = _run_policy(policy, upto)
-        clocks[f"{policy}_upto{upto}"] = sampler.summary()
+        per_rank = [None] * world
+        dist.all_gather_object(per_rank, sampler.summary(), group=group)
+        clocks[f"{policy}_upto{upto}"] = per_rank
         return out
 
     def _run_policy(policy, upto):
-        times, loads = [], []
+        times, loads, rows = [], [], []
         for s in range(total):
             flush.fill_(s & 255)
             dist.barrier(group=group)
@@ -111,7 +115,9 @@ def main():
                 load = torch.bincount(phys.reshape(-1) // pl, minlength=world).double()
                 dist.all_reduce(load, group=group)
                 loads.append(float(load.max() / load.mean()))
+                rows.append(float(load.max()))
         per_step = rank_max(times)
+        max_rows[f"{policy}_upto{upto}"] = sum(rows) / len(rows)
         return float(per_step.mean()), sum(loads) / len(loads)
 
     results = {}
@@ -132,10 +138,44 @@ def main():
     status = layer.check()
 
     if rank == 0:
-        rows = args.tokens * args.topk
-        remote = rows * (world - 1) / world * args.hidden * 2
+        n_rows = args.tokens * args.topk
+        remote = n_rows * (world - 1) / world * args.hidden * 2
         lp_ms, lp_load = results["lplb"]
         dispatch_ms = stages[1] - stages[0]
+        # roofline denominators: the driver-measured peaks of this pool when the file is there
+        peaks = {"bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback figures"}
+        peaks_file = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "MEASURED_PEAKS.json")
+        if os.path.exists(peaks_file):
+            with open(peaks_file) as fh:
+                measured = json.load(fh)
+            peaks = {"bf16_tflops": measured["bf16_tflops"], "bf16_tflops_sustained": measured["bf16_tflops_sustained"],
+                     "source": "MEASURED_PEAKS.json"}
+        rows_hot = max_rows["lplb_upto5"]  # rows on the most loaded rank, which sets the step time
+        flop1 = rows_hot * 2.0 * args.hidden * 2 * args.inter
+        flop2 = rows_hot * 2.0 * args.inter * args.hidden
+        gemm1_ms = stages[2] - (stages[0] if args.fuse_dispatch else stages[1])
+        gemm2_ms = stages[3] - stages[2]
+
+        def roof(flops, nvlink_bytes, ms):
+            """Achieved / roofline for a kernel inside the step loop: compute against the sustained
+            (power-capped) and the burst cuBLAS rate, NVLink at the nominal 900 GB/s per direction and
+            at the 770 GB/s that a peer copy reaches on this pool."""
+            out = {"ms": round(ms, 4), "tflops": round(flops / (ms * 1e-3) / 1e12, 1)}
+            for cname, cpeak in (("sustained", peaks["bf16_tflops_sustained"]), ("burst", peaks["bf16_tflops"])):
+                for lname, link in (("900", 900.0), ("770", 770.0)):
+                    bound_ms = max(flops / (cpeak * 1e12), nvlink_bytes / (link * 1e9)) * 1e3
+                    out[f"achieved_over_roofline_{cname}_nvlink{lname}"] = round(bound_ms / ms, 3)
+            return out
+
+        roofline = {
+            "peaks": dict(peaks, nvlink_gbs_nominal=900.0, nvlink_gbs_measured_peer_copy=770.0),
+            "rows_on_most_loaded_rank": round(rows_hot, 1),
+            "gemm2_with_combine": roof(flop2, remote, gemm2_ms),
+        }
+        if args.fuse_dispatch:
+            roofline["dispatch_with_gemm1"] = roof(flop1, remote, gemm1_ms)
+        else:
+            roofline["gemm1_swiglu"] = roof(flop1, 0.0, gemm1_ms)
         out = {
             "n_gpus": world,
             "fuse_dispatch": args.fuse_dispatch,
@@ -158,7 +198,8 @@ def main():
             "speedup_lplb_vs_none": round(results["none"][0] / lp_ms, 3),
             "speedup_lplb_vs_eplb": round(results["eplb"][0] / lp_ms, 3),
             "status": status,
-            "rank0_clocks_per_run": clocks,
+            "roofline": roofline,
+            "clocks_per_run_and_rank": clocks,
             "timing": "CUDA events per step around route + layer, 256 MiB L2 flush and a barrier before each step",
         }
         print(json.dumps(out))

@@ -250,7 +250,9 @@ class PlannerEngine {
     LPLB_CHECK(!use_exchange || n_ranks_ <= 32, "the in-kernel exchange covers at most 32 ranks");
     int& limit = is64 ? max_cta64_ : max_cta32_;
     if (limit < 0) limit = lplb::max_fused_ctas(topo(), prm_.solver, is64);
-    LPLB_CHECK(limit > 0, "fused kernel cannot be resident on this device");
+    LPLB_CHECK(limit >= 2, "fused kernel cannot be resident on this device");
+    // one CTA solves, the others count and redirect: a request for a single CTA still gets one worker
+    if (n_cta < 2) n_cta = 2;
     if (n_cta > limit) n_cta = limit;
     torch::Tensor out;
     if (out_opt.has_value()) {
@@ -272,7 +274,7 @@ class PlannerEngine {
                                  probs_.data_ptr<float>(), avail.data_ptr(), avail.scalar_type() == torch::kInt64,
                                  status_.data_ptr<int>(), out.data_ptr(), n_cta, grid_timeout_ns_,
                                  trace_.defined() ? reinterpret_cast<unsigned long long*>(trace_.data_ptr()) : nullptr,
-                                 cooperative_ ? 1 : 0, leader_mode_, stream()));
+                                 cooperative_ ? 1 : 0, stream()));
     return out;
   }
 
@@ -387,7 +389,6 @@ class PlannerEngine {
   // Cooperative launch (default) makes the driver guarantee that all CTAs of the fused kernel
   // are co-resident; an ordinary launch is cheaper but leaves that to the caller.
   void set_cooperative(bool on) { cooperative_ = on; }
-  void set_leader_mode(int mode) { leader_mode_ = mode; }
 
   // Phase stamps of the fused kernel (see fused_run_kernel): off by default.
   void enable_trace(bool on) {
@@ -466,7 +467,6 @@ class PlannerEngine {
   int n_ranks_ = 1, my_rank_ = 0, node_size_ = 0;
   bool exchange_open_ = false;
   bool cooperative_ = true;
-  int leader_mode_ = 0;
 };
 
 }  // namespace
@@ -502,7 +502,6 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def("close_exchange", &PlannerEngine::close_exchange)
       .def("exchange_open", &PlannerEngine::exchange_open)
       .def("set_cooperative", &PlannerEngine::set_cooperative)
-      .def("set_leader_mode", &PlannerEngine::set_leader_mode)
       .def("set_exchange_nodes", &PlannerEngine::set_exchange_nodes)
       .def("enable_trace", &PlannerEngine::enable_trace)
       .def("trace", &PlannerEngine::trace)

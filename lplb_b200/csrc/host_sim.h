@@ -152,6 +152,14 @@ inline int __all_sync(unsigned, int pred) {
   lplb_sim::g_warp->barrier.wait();
   return all;
 }
+inline int __any_sync(unsigned, int pred) {
+  lplb_sim::g_warp->pred[lplb_sim::g_lane] = pred;
+  lplb_sim::g_warp->barrier.wait();
+  int any = 0;
+  for (int l = 0; l < 32; ++l) any |= lplb_sim::g_warp->pred[l] != 0;
+  lplb_sim::g_warp->barrier.wait();
+  return any;
+}
 inline double rsqrt(double x) { return 1.0 / std::sqrt(x); }
 inline float __fdividef(float a, float b) { return a / b; }
 

@@ -29,13 +29,6 @@
 
 namespace lplb {
 
-#ifdef LPLB_BLK_PROFILE
-__device__ unsigned long long g_blk_prof[16];
-#define BLK_T0() const long long prof_t0_ = clock64()
-#define BLK_ACC(k, since) do { if (tid == 0) g_blk_prof[k] += (unsigned long long)(clock64() - (since)); } while (0)
-#else
-#define BLK_ACC(k, since) do { } while (0)
-#endif
 
 constexpr int kBlkThreads = 256;
 constexpr int kBlkWarps = kBlkThreads / 32;
@@ -131,10 +124,10 @@ __device__ __forceinline__ double pivot_rcp(double x) {
 __device__ __forceinline__ constexpr int tri8(int i, int k) { return i * (i + 1) / 2 + k; }
 
 // In: `a` = lower triangle of a symmetric positive definite 8 x 8 block.  Out: strictly lower
-// part of `a` = unit lower L of a = L D L^T, dinv = 1/D, strictly lower part of `w` = L^-1.
-// Straight-line code with static register indices.  A pivot that rounding drove non-positive
-// or non-finite is replaced by a huge one, which zeroes that unknown in the solves.
-__device__ __forceinline__ void blk8_factor(double (&a)[36], double (&dinv)[8], double (&w)[36]) {
+// part of `a` = unit lower L of a = L D L^T, dinv = 1/D.  Straight-line code with static
+// register indices.  A pivot that rounding drove non-positive or non-finite is replaced by a
+// huge one, which zeroes that unknown in the solves.
+__device__ __forceinline__ void blk8_factor(double (&a)[36], double (&dinv)[8]) {
 #pragma unroll
   for (int j = 0; j < 8; ++j) {
     double piv = a[tri8(j, j)];
@@ -149,6 +142,10 @@ __device__ __forceinline__ void blk8_factor(double (&a)[36], double (&dinv)[8], 
 #pragma unroll
     for (int i = j + 1; i < 8; ++i) a[tri8(i, j)] *= dinv[j];
   }
+}
+
+// Strictly lower part of `w` = inverse of the unit lower L held in the strictly lower part of `a`.
+__device__ __forceinline__ void blk8_invert(const double (&a)[36], double (&w)[36]) {
 #pragma unroll
   for (int c = 0; c < 8; ++c)
 #pragma unroll
@@ -163,6 +160,12 @@ __device__ __forceinline__ void blk8_factor(double (&a)[36], double (&dinv)[8], 
 // Factor the matrix in shared memory (lower triangle of N in `mat`), all kBlkThreads threads.
 // On return: wblk holds W_k = L_kk^-1 per diagonal block, dinv holds 1/D, and below the
 // diagonal blocks `mat` holds L_ik W_k.  The diagonal blocks of `mat` are left as they were.
+//
+// Per block column the dependent chain is: diagonal block (every thread of the panel warps
+// factors it for itself, no hand-over), the rows below it (one thread per row: L and L D of the
+// row), a barrier, the trailing update by all threads, a barrier.  What the chain does not need
+// runs beside it: another warp inverts the diagonal block and stores W_k, and the products
+// L_ik W_k that the substitutions use are formed by all threads next to the trailing update.
 __device__ __forceinline__ void blk_factor(const int tid, const BlkLayout& l, double* sm) {
   double* mat = sm + l.mat;
   double* wblk = sm + l.wblk;
@@ -172,59 +175,43 @@ __device__ __forceinline__ void blk_factor(const int tid, const BlkLayout& l, do
   const int warp = tid >> 5, ld = l.ld;
   for (int kb = 0; kb < l.nb; ++kb) {
     const int k0 = kb * 8, r0 = k0 + 8, m = l.gp - r0;  // m rows below this block column
-    const int panel_warps = m > 0 ? (m + 31) >> 5 : 1;
-#ifdef LPLB_BLK_PROFILE
-    long long ft = clock64();
-#endif
-    if (warp < panel_warps) {
-      // every thread of these warps factors the diagonal block for itself: no hand-over
-      double a[36], dinv[8], w[36];
+    const int panel_warps = (m + 31) >> 5;               // warps 0 .. panel_warps-1 own the rows below
+    const int inv_warp = panel_warps;                    // the next warp inverts the diagonal block
+    if (warp <= inv_warp) {
+      double a[36], dinv[8];
 #pragma unroll
       for (int i = 0; i < 8; ++i)
 #pragma unroll
         for (int k = 0; k <= i; ++k) a[tri8(i, k)] = mat[(k0 + i) * ld + k0 + k];
-      blk8_factor(a, dinv, w);
-      if (warp == 0) {  // same values from every lane
+      blk8_factor(a, dinv);
+      if (warp == inv_warp) {  // same values from every lane
+        double w[36];
+        blk8_invert(a, w);
 #pragma unroll
         for (int i = 1; i < 8; ++i)
 #pragma unroll
           for (int k = 0; k < i; ++k) wblk[(k0 + i) * kPanelLd + k] = w[tri8(i, k)];
 #pragma unroll
         for (int j = 0; j < 8; ++j) dinvs[k0 + j] = dinv[j];
-      }
-      if (tid < m) {
+      } else if (tid < m) {
+        // row of the panel: x = A_row L_kk^-T = (L D)_row by substitution, L_row = x / D
         const int row = r0 + tid;
-        double ar[8], x[8], lr[8];
+        double x[8];
 #pragma unroll
-        for (int c = 0; c < 8; ++c) ar[c] = mat[row * ld + k0 + c];
-        // X = A_row L_kk^-T = (L D)_row;  L_row = X / D;  stored product = L_row W_k
+        for (int c = 0; c < 8; ++c) x[c] = mat[row * ld + k0 + c];
 #pragma unroll
-        for (int c = 0; c < 8; ++c) {
-          double acc = ar[c];
+        for (int c = 1; c < 8; ++c)
 #pragma unroll
-          for (int k = 0; k < c; ++k) acc = fma(ar[k], w[tri8(c, k)], acc);
-          x[c] = acc;
-          lr[c] = acc * dinv[c];
-        }
+          for (int k = 0; k < c; ++k) x[c] = fma(-x[k], a[tri8(c, k)], x[c]);
 #pragma unroll
         for (int c = 0; c < 8; ++c) {
-          double acc = lr[c];
-#pragma unroll
-          for (int k = c + 1; k < 8; ++k) acc = fma(lr[k], w[tri8(k, c)], acc);
-          mat[row * ld + k0 + c] = acc;
-          pl[row * kPanelLd + c] = lr[c];
           px[row * kPanelLd + c] = x[c];
+          pl[row * kPanelLd + c] = x[c] * dinv[c];
         }
       }
     }
-#ifdef LPLB_BLK_PROFILE
-    BLK_ACC(4, ft); ft = clock64();
-#endif
     __syncthreads();
     if (m == 0) break;
-#ifdef LPLB_BLK_PROFILE
-    BLK_ACC(10, ft); ft = clock64();
-#endif
     // trailing update of the lower triangle: A_ij -= sum_c L_ic (L D)_jc
     const int ti = tid >> 4, tj = tid & 15;
     for (int i = ti; i < m; i += 16) {
@@ -241,13 +228,16 @@ __device__ __forceinline__ void blk_factor(const int tid, const BlkLayout& l, do
         mat[row * ld + col] = acc;
       }
     }
-#ifdef LPLB_BLK_PROFILE
-    BLK_ACC(5, ft); ft = clock64();
-#endif
+    // what the substitutions read below this diagonal block: (L_ik W_k)[row][c] = sum_j L[row][j] W_k[j][c]
+    // (W_k has a unit diagonal and zeros above it, so the full sum needs no case distinction)
+    for (int t = tid; t < m * 8; t += kBlkThreads) {
+      const int row = r0 + (t >> 3), c = t & 7;
+      double acc = 0.0;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc = fma(pl[row * kPanelLd + j], wblk[(k0 + j) * kPanelLd + c], acc);
+      mat[row * ld + k0 + c] = acc;
+    }
     __syncthreads();
-#ifdef LPLB_BLK_PROFILE
-    BLK_ACC(11, ft);
-#endif
   }
 }
 
@@ -346,10 +336,19 @@ __device__ __forceinline__ void blk_solve(const int tid, const BlkLayout& l, dou
 // block_solver_smem_bytes(g, D) of shared memory.  The outcome is the same on every row
 // thread; f_out is meaningful on threads tid < g.
 template <int D>
-__device__ IpmOutcome ipm_solve_block(const int tid, const int g, const double (&w_in)[D], const double fixed,
-                                      const int (&src)[D], const int (&dst)[D], const IpmParams prm,
-                                      double (&f_out)[D], double* anchor, int* anchor_valid, double* sm) {
+__device__ __forceinline__ IpmOutcome ipm_solve_block(const int tid, const int g, const double (&w_in)[D],
+                                                      const double fixed, const int (&src_in)[D],
+                                                      const int (&dst_in)[D], const IpmParams prm, double (&f_out)[D],
+                                                      double* anchor, int* anchor_valid, double* sm) {
   constexpr double kEta = 0.995;
+  // Private copies: when this function is not inlined the caller's arrays live in local memory,
+  // and every use in the loop would be a load that has to be repeated after each store.
+  int src[D], dst[D];
+#pragma unroll
+  for (int d = 0; d < D; ++d) {
+    src[d] = src_in[d];
+    dst[d] = dst_in[d];
+  }
   const BlkLayout l = blk_layout(g, D);
   const int warp = tid >> 5, lane = tid & 31;
   const int n32 = l.gp32, rw = l.r_warps;
@@ -443,19 +442,32 @@ __device__ IpmOutcome ipm_solve_block(const int tid, const int g, const double (
   // ---- warm start from the anchor, if it still fits the data -----------------------------
   bool cold = true;
   {
+    // The slot is read whether or not it is valid (it is always allocated), so that its loads
+    // and the load of the flag are in flight together instead of one behind the other.
     double fa[D], va[D], za[D], qa[D], sa = 1.0, ya = 1.0 / g, ta = 0.0;
-    const bool have = live && anchor != nullptr && anchor_valid != nullptr && *anchor_valid != 0;
+    const bool slot = live && anchor != nullptr && anchor_valid != nullptr;
 #pragma unroll
     for (int d = 0; d < D; ++d) {
-      fa[d] = have ? anchor[d] : 0.5;
-      va[d] = have ? anchor[D + d] : 0.5;
-      za[d] = have ? anchor[2 * D + d] : 1.0;
-      qa[d] = have ? anchor[3 * D + d] : 1.0;
+      fa[d] = slot ? anchor[d] : 0.5;
+      va[d] = slot ? anchor[D + d] : 0.5;
+      za[d] = slot ? anchor[2 * D + d] : 1.0;
+      qa[d] = slot ? anchor[3 * D + d] : 1.0;
     }
-    if (have) {
+    if (slot) {
       sa = anchor[4 * D];
       ya = anchor[4 * D + 1];
       ta = anchor[4 * D + 2];
+    }
+    const bool have = slot && *anchor_valid != 0;
+    if (!have) {
+#pragma unroll
+      for (int d = 0; d < D; ++d) {
+        fa[d] = va[d] = 0.5;
+        za[d] = qa[d] = 1.0;
+      }
+      sa = 1.0;
+      ya = 1.0 / g;
+      ta = 0.0;
     }
     const double mfa = m_times(fa, x_rhs);
     double r[3] = {have ? 1.0 : 0.0, have ? fabs(ta - base - mfa - sa) : 0.0, have ? ta : -1e300};
@@ -484,9 +496,6 @@ __device__ IpmOutcome ipm_solve_block(const int tid, const int g, const double (
   double gap = 1e300, gap_scale = 1.0;
 
   for (int it = 0;; ++it) {
-#ifdef LPLB_BLK_PROFILE
-    long long pt = clock64();
-#endif
     // ---- residuals, gap, stopping test ---------------------------------------------
 #pragma unroll
     for (int d = 0; d < D; ++d) x_wf[d * n32 + tid] = w[d] * f[d];
@@ -538,9 +547,6 @@ __device__ IpmOutcome ipm_solve_block(const int tid, const int g, const double (
       saved = true;
     }
     const bool go = !done && it < prm.max_iters;
-#ifdef LPLB_BLK_PROFILE
-    BLK_ACC(0, pt); pt = clock64();
-#endif
 
     // ---- normal matrix, one row per rank --------------------------------------------------
     double inv_f[D], inv_v[D], theta[D];
@@ -594,19 +600,9 @@ __device__ IpmOutcome ipm_solve_block(const int tid, const int g, const double (
       }
     }
     if (tid == 0) ctrl[0] = go ? 1 : 0;
-#ifdef LPLB_BLK_PROFILE
-    BLK_ACC(1, pt); pt = clock64();
-#endif
     __syncthreads();
     if (!go) break;
-#ifdef LPLB_BLK_PROFILE
-    BLK_ACC(2, pt); pt = clock64();
-#endif
     blk_factor(tid, l, sm);
-#ifdef LPLB_BLK_PROFILE
-    BLK_ACC(3, pt); pt = clock64();
-    if (tid == 0) g_blk_prof[9] += 1;
-#endif
 
     // ---- predictor (pass 0) and corrector (pass 1) share one body ------------------------
     double df[D], dv[D], dz[D], dq[D], ds = 0.0, dy = 0.0, dt = 0.0;
@@ -630,9 +626,6 @@ __device__ IpmOutcome ipm_solve_block(const int tid, const int g, const double (
 #pragma unroll
       for (int d = 0; d < D; ++d) acc += w[d] * theta[d] * rd_t[d] - x_rhs[d * n32 + src[d]];
       double a = live ? acc - r_p + r_sy * inv_y : 0.0;
-#ifdef LPLB_BLK_PROFILE
-      BLK_ACC(6, pt); pt = clock64();
-#endif
       if (pass == 0) {
         double b2 = live ? 1.0 : 0.0;  // N b = 1: the border column that carries sum(dy) = r_t
         blk_solve<true>(tid, l, sm, a, b2);
@@ -641,9 +634,6 @@ __device__ IpmOutcome ipm_solve_block(const int tid, const int g, const double (
         double unused = 0.0;
         blk_solve<false>(tid, l, sm, a, unused);
       }
-#ifdef LPLB_BLK_PROFILE
-      BLK_ACC(7, pt); pt = clock64();
-#endif
       {
         double r[2] = {live ? a : 0.0, live ? border : 0.0};
         rows_reduce<2, 0u>(r, l, sm, warp, lane, red_phase);
@@ -686,9 +676,6 @@ __device__ IpmOutcome ipm_solve_block(const int tid, const int g, const double (
         apf = -r[0];
         adf = -r[1];
       }
-#ifdef LPLB_BLK_PROFILE
-      BLK_ACC(8, pt); pt = clock64();
-#endif
     }
     const double ap = fmin(kEta * apf, 1.0), ad = fmin(kEta * adf, 1.0);
     t += ap * dt;

@@ -46,6 +46,11 @@ struct IpmParams {
   int* anchor_valid = nullptr;  // [n_group]
   double guard = 0.05;
   double snap_mu = 1e-3;
+  // Rehearsal (optional): a solve on made-up data whose only purpose is to pull the solver's
+  // code into the instruction caches before the real statistics are there.  It leaves at the
+  // next check after `*stop` (a word in shared memory that another warp sets) becomes
+  // non-zero.  Null for every real solve.
+  const volatile int* stop = nullptr;
 };
 
 struct IpmOutcome {
@@ -204,6 +209,9 @@ __device__ __forceinline__ double ldl8_solve(const Ldl8& m, int li, double g) {
 }
 
 // All 32 lanes must call this together.  `li` is the lane's index inside its segment.
+// Always inlined into its caller: left to the compiler, the decision changed from build to build
+// with unrelated edits elsewhere in the translation unit, and a solve ran 2 to 4 us slower
+// whenever the function ended up out of line.
 //   w[d]      load of own bundle d (any non-negative unit)
 //   fixed     load of the lane's non-replicated experts (same unit)
 //   src[d]    segment lane whose bundle d this rank holds a replica of  (r2o[i][d])
@@ -213,11 +221,20 @@ __device__ __forceinline__ double ldl8_solve(const Ldl8& m, int li, double g) {
 // `anchor` / `anchor_valid`: this lane's slot of the warm-start state and its group's flag
 // (both null when warm starts are off or the lane is padding).
 template <int GP, int D>
-__device__ IpmOutcome ipm_solve_segment(int li, const double (&w_in)[D], double fixed, const int (&src)[D],
-                                        const int (&dst)[D], const IpmParams prm, double (&f_out)[D],
-                                        double* anchor = nullptr, int* anchor_valid = nullptr) {
+__device__ __forceinline__ IpmOutcome ipm_solve_segment(int li, const double (&w_in)[D], double fixed, const int (&src_in)[D],
+                                                        const int (&dst_in)[D], const IpmParams prm,
+                                                        double (&f_out)[D], double* anchor = nullptr,
+                                                        int* anchor_valid = nullptr) {
   constexpr double kEta = 0.995;
   constexpr int kComp = GP + 2 * GP * D;
+  // Private copies: when this function is not inlined the caller's arrays live in local memory,
+  // and every use in the loop would be a load that has to be repeated after each store.
+  int src[D], dst[D];
+#pragma unroll
+  for (int d = 0; d < D; ++d) {
+    src[d] = src_in[d];
+    dst[d] = dst_in[d];
+  }
 
   // ---- scale so that the mean rank load is 1 ---------------------------------------
   double mine = fixed;
@@ -271,19 +288,32 @@ __device__ IpmOutcome ipm_solve_segment(int li, const double (&w_in)[D], double 
   // The decision is taken per segment; lanes without a slot (padding) follow their segment.
   bool cold = true;
   {
+    // The slot is read whether or not it is valid (it is always allocated), so that its loads
+    // and the load of the flag are in flight together instead of one behind the other.
     double fa[D], va[D], za[D], qa[D], sa = 1.0, ya = 1.0 / GP, ta = 0.0;
-    const bool have = anchor != nullptr && anchor_valid != nullptr && *anchor_valid != 0;
+    const bool slot = anchor != nullptr && anchor_valid != nullptr;
 #pragma unroll
     for (int d = 0; d < D; ++d) {
-      fa[d] = have ? anchor[d] : 0.5;
-      va[d] = have ? anchor[D + d] : 0.5;
-      za[d] = have ? anchor[2 * D + d] : 1.0;
-      qa[d] = have ? anchor[3 * D + d] : 1.0;
+      fa[d] = slot ? anchor[d] : 0.5;
+      va[d] = slot ? anchor[D + d] : 0.5;
+      za[d] = slot ? anchor[2 * D + d] : 1.0;
+      qa[d] = slot ? anchor[3 * D + d] : 1.0;
     }
-    if (have) {
+    if (slot) {
       sa = anchor[4 * D];
       ya = anchor[4 * D + 1];
       ta = anchor[4 * D + 2];
+    }
+    const bool have = slot && *anchor_valid != 0;
+    if (!have) {
+#pragma unroll
+      for (int d = 0; d < D; ++d) {
+        fa[d] = va[d] = 0.5;
+        za[d] = qa[d] = 1.0;
+      }
+      sa = 1.0;
+      ya = 1.0 / GP;
+      ta = 0.0;
     }
     const double mfa = m_times(fa);  // shuffles inside: every lane takes part, with or without a slot
     const double rp = have ? fabs(ta - base - mfa - sa) : 0.0;
@@ -314,7 +344,12 @@ __device__ IpmOutcome ipm_solve_segment(int li, const double (&w_in)[D], double 
   int iters = 0;
   double gap = 1e300, gap_scale = 1.0;
 
+  // one shared-memory read for the whole warp, so every lane takes the same way out
+  auto told_to_stop = [&]() -> bool { return prm.stop != nullptr && __any_sync(0xffffffffu, *prm.stop != 0); };
+  bool halted = false;
+
   for (int it = 0; it <= prm.max_iters; ++it) {
+    if (told_to_stop()) break;
     // ---- residuals, gap, stopping test ---------------------------------------------
     const double mf = m_times(f);
     const double r_p = t - base - mf - s;
@@ -391,6 +426,7 @@ __device__ IpmOutcome ipm_solve_segment(int li, const double (&w_in)[D], double 
       }
     }
 
+    if (told_to_stop()) break;
     // ---- factorisation -------------------------------------------------------------------
     Ldl8 dense;
     if constexpr (GP == 8) ldl8_factor(row, dense);
@@ -405,6 +441,10 @@ __device__ IpmOutcome ipm_solve_segment(int li, const double (&w_in)[D], double 
     float apf = 0.f, adf = 0.f;
 #pragma unroll 1
     for (int pass = 0; pass < 2; ++pass) {
+      if (told_to_stop()) {
+        halted = true;
+        break;
+      }
       // complementarity targets: -XZe for the predictor, sigma*mu*e - XZe - dXdZe after it
       const double r_sy = sm - s * y - ds * dy;
       double r_zf[D], r_qv[D], rd_t[D];
@@ -455,6 +495,7 @@ __device__ IpmOutcome ipm_solve_segment(int li, const double (&w_in)[D], double 
         sm = ratio * ratio * ratio * mu;
       }
     }
+    if (halted) break;
     const double ap = fmin(kEta * (double)apf, 1.0), ad = fmin(kEta * (double)adf, 1.0);
     if (!done) {
       t += ap * dt;
@@ -496,7 +537,8 @@ __device__ IpmOutcome ipm_solve_segment(int li, const double (&w_in)[D], double 
 // Out-of-line entry for the 32-rank instantiation.  Inlined into a kernel, the 32-register-pair
 // matrix row plus the caller's own state no longer fit the register file and the compiler
 // moves the row to local memory, which costs an order of magnitude; as a separate function
-// the solver gets the whole register budget to itself.
+// the solver gets the whole register budget to itself.  The smaller instantiations are inlined:
+// out of line they measured about 2 us slower per solve.
 template <int GP, int D>
 __device__ __noinline__ IpmOutcome ipm_solve_segment_ool(int li, const double (&w_in)[D], double fixed,
                                                          const int (&src)[D], const int (&dst)[D],

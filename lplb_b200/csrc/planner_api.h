@@ -77,14 +77,15 @@ cudaError_t launch_redirect(const void* idx, int idx_is64, long long n, const fl
 cudaError_t launch_exchange(const int* in, int n_logical, const ExchangeDesc& ex, void* workspace, int* out,
                             int* status, cudaStream_t stream);
 
-// Single-launch count + exchange + solve + redirect.  Cooperative launch: n_cta must not
-// exceed max_fused_ctas().  `trace` (may be null) receives 8 globaltimer stamps, see the kernel.
+// Single-launch count + exchange + solve + redirect.  n_cta >= 2: CTA 0 exchanges and solves,
+// the other n_cta - 1 CTAs count and redirect.  Cooperative launch: n_cta must not exceed
+// max_fused_ctas().  `trace` (may be null) receives 8 globaltimer stamps, see the kernel.
 // cooperative = 0 uses an ordinary launch: no co-residency guarantee from the driver, so the
 // caller must know the GPU has room for n_cta CTAs (the in-kernel waits stay bounded).
 cudaError_t launch_fused(const void* idx, int idx_is64, long long n, const TopoDesc& topo, const ExchangeDesc& ex,
                          SolveParams prm, void* workspace, float* probs, void* avail, int avail_is64, int* status,
                          void* out, int n_cta, unsigned long long grid_timeout_ns, unsigned long long* trace,
-                         int cooperative, int leader_mode, cudaStream_t stream);
+                         int cooperative, cudaStream_t stream);
 
 // Co-resident CTA limit of the fused kernel for this topology on the current device (0 when the
 // shape has no device solver or its tables do not fit shared memory).

@@ -40,14 +40,15 @@ struct Exchange {
 
 // Per-engine scratch in this GPU's memory; zero-initialised by the host once.
 struct Workspace {
-  uint32_t epoch;     // launches completed
-  uint32_t arrive;    // CTAs of the running launch that published their counts
-  uint32_t lp_done;   // epoch whose shares are ready
-  uint32_t exit_cnt;  // CTAs of the running launch that finished
+  uint32_t epoch;      // launches completed
+  uint32_t arrive[2];  // by launch parity: CTAs of that launch that published their counts
+  uint32_t lp_done;    // epoch whose shares are ready
   uint32_t count_ticket;  // used by the stand-alone counting kernel
-  uint32_t pad[3];
+  uint32_t exit_cnt;   // tracing only: CTAs of the running launch that finished
+  uint32_t pad[2];
   // followed by: int total[2][E]; int global_cnt[E];
 };
+static_assert(sizeof(Workspace) == 32, "the tables that follow the header start at byte 32");
 __host__ __device__ inline size_t workspace_bytes(int e) { return sizeof(Workspace) + sizeof(int) * 3 * (size_t)e; }
 __device__ __forceinline__ int* ws_total(Workspace* ws, int parity, int e) {
   return reinterpret_cast<int*>(ws + 1) + (size_t)parity * e;
@@ -293,7 +294,7 @@ __device__ __forceinline__ void report_group(const IpmOutcome& res, int grp, Cou
 
 // Warp solver: each warp carries 32/GP groups; a CTA covers `kWarps * 32/GP` groups per round.
 template <int GP, int D>
-__device__ void solve_groups(const int* __restrict__ bundle, const Topo& tp, int first_group, int group_stride,
+__device__ __forceinline__ void solve_groups(const int* __restrict__ bundle, const Topo& tp, int first_group, int group_stride,
                              IpmParams prm, float* __restrict__ probs, Counter avail, int* status) {
   constexpr int kSeg = 32 / GP;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -342,7 +343,7 @@ __device__ void solve_groups(const int* __restrict__ bundle, const Topo& tp, int
 // instantiated replica count; slots tp.d..DP-1 are self edges of weight zero.  `scratch` is
 // block_solver_smem_bytes(tp.g, DP) of shared memory, 8-byte aligned.
 template <int DP>
-__device__ void solve_groups_block(const int* __restrict__ bundle, const Topo& tp, int first_group, int group_stride,
+__device__ __forceinline__ void solve_groups_block(const int* __restrict__ bundle, const Topo& tp, int first_group, int group_stride,
                                    IpmParams prm, float* __restrict__ probs, Counter avail, int* status,
                                    double* scratch) {
   const int tid = threadIdx.x, dd = tp.d;
@@ -509,6 +510,13 @@ struct ExchangeShared {
   unsigned missing;  // peers that never arrived
   unsigned marked;   // peers whose vector carried the sender's `degraded` mark
 };
+// Barrier among the first NT threads of the CTA (all of them: the ordinary block barrier).
+template <int NT>
+__device__ __forceinline__ void team_sync() {
+  if constexpr (NT == kBlock) __syncthreads();
+  else asm volatile("bar.sync 2, %0;" ::"n"(NT) : "memory");
+}
+
 __device__ __forceinline__ void exchange_prepare(const Exchange& ex, ExchangeShared* xs) {
   if (threadIdx.x < kMaxRanks) xs->recv[threadIdx.x] = (int)threadIdx.x < ex.n_ranks && ex.recv != nullptr ? ex.recv[threadIdx.x] : nullptr;
   if (threadIdx.x == 0) xs->missing = xs->marked = 0;
@@ -523,6 +531,8 @@ __device__ __forceinline__ void exchange_prepare(const Exchange& ex, ExchangeSha
 // xs->marked, which the caller folds into the report once the level has ended.
 // `xtrace` (thread 0 only, may be null) receives four stamps: own pushes issued, first and
 // last word of another peer seen (for element 0), and that last peer's rank.
+// Called by the first NT threads of the CTA.
+template <int NT>
 __device__ __forceinline__ void exchange_level(const Exchange& ex, ExchangeShared* xs, uint32_t epoch, int e, int level,
                                                int first_peer, int stride, int n_peers, int* vec, bool degraded,
                                                int* status, unsigned long long* xtrace) {
@@ -533,7 +543,7 @@ __device__ __forceinline__ void exchange_level(const Exchange& ex, ExchangeShare
   // ---- push: all peers' stores are issued back to back, nothing waits in between -----------
   if ((e & 1) == 0) {
     const int half = e >> 1, items = n_peers * half;
-    for (int it = threadIdx.x; it < items; it += kBlock) {
+    for (int it = threadIdx.x; it < items; it += NT) {
       const int j = it / half, pr = it - j * half, r = first_peer + j * stride;
       if (!LPLB_CHECKED(r, ex.n_ranks, status, kPhExchange)) continue;
       const uint32_t mark = (degraded && pr == 0) ? 0x80000000u : 0u;
@@ -542,7 +552,7 @@ __device__ __forceinline__ void exchange_level(const Exchange& ex, ExchangeShare
     }
   } else {
     const int items = n_peers * e;
-    for (int it = threadIdx.x; it < items; it += kBlock) {
+    for (int it = threadIdx.x; it < items; it += NT) {
       const int j = it / e, i = it - j * e, r = first_peer + j * stride;
       if (!LPLB_CHECKED(r, ex.n_ranks, status, kPhExchange)) continue;
       const uint32_t mark = (degraded && i == 0) ? 0x80000000u : 0u;
@@ -551,13 +561,13 @@ __device__ __forceinline__ void exchange_level(const Exchange& ex, ExchangeShare
   }
   const bool stamping = xtrace != nullptr && threadIdx.x == 0;
   if (stamping) xtrace[0] = global_timer_ns();
-  __syncthreads();  // every thread has read the `vec` entries it pushes; they may be overwritten now
+  team_sync<NT>();  // every thread has read the `vec` entries it pushes; they may be overwritten now
   // ---- poll and sum: one pass over all peers per element, kPollChunk loads in flight --------
   const unsigned long long* base = xs->recv[ex.my_rank] + level_base * e;
   unsigned late = 0;
   bool seen_any = false;
   const uint64_t t0 = global_timer_ns();
-  for (int i = threadIdx.x; i < e; i += kBlock) {
+  for (int i = threadIdx.x; i < e; i += NT) {
     int acc = 0;
     for (int j0 = 0; j0 < n_peers; j0 += kPollChunk) {
       const int nj = min(kPollChunk, n_peers - j0);
@@ -602,12 +612,12 @@ __device__ __forceinline__ void exchange_level(const Exchange& ex, ExchangeShare
     vec[i] = acc;
   }
   if (late) atomicOr(&xs->missing, late);
-  __syncthreads();
+  team_sync<NT>();
   const unsigned miss = xs->missing;
   if (miss) {
     // Rare path: a peer is absent for at least one element, so it is absent for all of them.
     // This rank's own vector is still in its own slot of the receive buffer.
-    for (int i = threadIdx.x; i < e; i += kBlock) {
+    for (int i = threadIdx.x; i < e; i += NT) {
       const int own = (int)((uint32_t)ld_volatile_u64(&base[(size_t)ex.my_rank * e + i]) & 0x7FFFFFFFu);
       int acc = 0;
       for (int j = 0; j < n_peers; ++j) {
@@ -618,7 +628,7 @@ __device__ __forceinline__ void exchange_level(const Exchange& ex, ExchangeShare
       }
       vec[i] = acc;
     }
-    __syncthreads();
+    team_sync<NT>();
   }
 }
 
@@ -629,17 +639,18 @@ __device__ __forceinline__ void exchange_level(const Exchange& ex, ExchangeShare
 // among the ranks with the same position in every node; (node_size - 1) + (n_nodes - 1)
 // partners instead of n_ranks - 1.  Returns a bit mask of the peers that never arrived or sent
 // a marked vector.  exchange_prepare must have run, followed by a block barrier.
+template <int NT>
 __device__ __forceinline__ unsigned exchange_counts(const Exchange& ex, ExchangeShared* xs, uint32_t epoch, int e,
                                                     int* vec, int* status, unsigned long long* xtrace) {
   const int s = ex.node_size;
   if (s <= 0 || s >= ex.n_ranks) {
-    exchange_level(ex, xs, epoch, e, 0, 0, 1, ex.n_ranks, vec, false, status, xtrace);
+    exchange_level<NT>(ex, xs, epoch, e, 0, 0, 1, ex.n_ranks, vec, false, status, xtrace);
   } else {
     const int node = ex.my_rank / s, local = ex.my_rank - node * s;
-    exchange_level(ex, xs, epoch, e, 0, node * s, 1, s, vec, false, status, xtrace);
+    exchange_level<NT>(ex, xs, epoch, e, 0, node * s, 1, s, vec, false, status, xtrace);
     const bool degraded = xs->missing != 0;  // every thread reads it after the level's closing barrier
-    exchange_level(ex, xs, epoch, e, 1, local, s, ex.n_ranks / s, vec, degraded, status,
-                   xtrace != nullptr ? xtrace + 4 : nullptr);
+    exchange_level<NT>(ex, xs, epoch, e, 1, local, s, ex.n_ranks / s, vec, degraded, status,
+                       xtrace != nullptr ? xtrace + 4 : nullptr);
   }
   return xs->missing | xs->marked;  // both final: the last level ended with a block barrier
 }
@@ -661,86 +672,200 @@ __global__ void __launch_bounds__(kBlock) exchange_kernel(const int* __restrict_
     other[i] = 0;
   }
   __syncthreads();
-  const unsigned miss = exchange_counts(ex, &xs, epoch, e, vec, status, nullptr);
+  const unsigned miss = exchange_counts<kBlock>(ex, &xs, epoch, e, vec, status, nullptr);
   if (miss && threadIdx.x == 0) {
     atomicAdd(&status[kStTimeouts], 1);
     raise_status(status, kErrPeerTimeout, kPhExchange, (int)miss);
   }
   for (int i = threadIdx.x; i < e; i += kBlock) out[i] = vec[i];
   __syncthreads();
-  if (threadIdx.x == 0) st_release_gpu(&ws->epoch, epoch);
+  if (threadIdx.x == 0) {
+    ws->arrive[(epoch & 1) ^ 1] = 0;  // every launch leaves the next one's arrival counter at zero
+    st_release_gpu(&ws->epoch, epoch);
+  }
 }
 
 // ---------------------------------------------------------------------------------------
 // Single-launch planner step.  Launched cooperatively so that all CTAs are co-resident.
 //
-//   every CTA   : histogram its slice; reserve an ordinal range per expert with one
-//                 returning atomicAdd on the rank-local totals; take an arrival ticket.
-//   last ticket : that CTA knows that every count is in.  It exchanges the totals with the
-//                 peers, solves the LPs, publishes the shares and raises lp_done.  Nobody polls
-//                 for the arrivals.
-//   every CTA   : wait for lp_done; turn shares into integer quotas; rewrite its slice.
+//   CTAs 1..n  ("workers"): histogram their slice of the indices; reserve an ordinal range per
+//                expert with one returning atomicAdd on the rank-local totals; arrive.
+//   CTA 0      ("solver"):  meanwhile pulls the solver's inputs into its caches; waits for the
+//                arrivals; exchanges the totals with the peers; solves the LPs; publishes the
+//                shares; raises lp_done.
+//   workers:     wait for lp_done; turn shares into integer quotas; rewrite their slice.
 //
-// The ordinal ranges come from atomics, so which CTA gets which range differs from run
-// to run; quotas are exact regardless.  Shared memory: the five E-sized redirect tables, the
-// (D + 1) bundle sums per rank, and for GP == 0 the scratch area of the thread-block solver.
-// GP = 8, 16, 32 selects the warp solver for groups of up to GP ranks, GP = 0 the thread-block
-// solver for any group size; D is the instantiated replica count (>= tp.d when GP == 0).
+// The solver CTA touches no indices.  Its code path shares no registers with the workers' (the
+// workers keep indices and table pointers live across their wait; inlined into one path with
+// the solver they cost it the registers it needs for its own instruction-level parallelism),
+// and because it is always CTA 0 the solver's code, some two thousand straight-line
+// instructions per iteration, stays in one SM's instruction cache from launch to launch.  Both
+// were measured: with the CTA that delivers the last counts doing the solve instead, on
+// whichever SM that is, the step's 90th percentile went from 27 to 41 us.
+//
+// The ordinal ranges come from atomics, so which worker gets which range differs from run
+// to run; quotas are exact regardless.  Shared memory: the five E-sized redirect tables
+// (workers) or the statistics vector (solver), the (D + 1) bundle sums per rank, and for
+// GP == 0 the scratch area of the thread-block solver.  GP = 8, 16, 32 selects the warp solver
+// for groups of up to GP ranks, GP = 0 the thread-block solver for any group size; D is the
+// instantiated replica count (>= tp.d when GP == 0).
 constexpr int kTraceWords = 16;
 
-template <int GP, int D, typename IdxT>
-__global__ void __launch_bounds__(kBlock) fused_run_kernel(const IdxT* __restrict__ idx, long long n, Topo tp,
-                                                           Exchange ex, IpmParams prm, Workspace* ws,
-                                                           float* __restrict__ probs, Counter avail, int* status,
-                                                           IdxT* __restrict__ out, unsigned long long grid_timeout_ns,
-                                                           unsigned long long* __restrict__ trace, int leader_mode) {
-  extern __shared__ __align__(16) int smem[];
-  const int e = tp.e, p = blockIdx.x, n_cta = gridDim.x;
-  // Optional phase stamps (globaltimer, ns): 0 start (CTA 0), 1 CTA 0 counted its slice, 2 the
-  // last count arrived, 3 statistics exchanged, 4 LPs solved (2-4 by the CTA with the last
-  // ticket), 5 CTA 0 redirected its slice, 6 last CTA left; 8-11 and 12-15 the stamps of the
-  // two exchange levels (see exchange_level).
+// Optional phase stamps (globaltimer, ns): 0 solver CTA started, 1 first worker arrived, 2 all
+// counts in, 3 statistics exchanged, 4 LPs solved, 5 first worker redirected its slice, 6 last
+// worker left; 8-11 and 12-15 the stamps of the two exchange levels (see exchange_level).
+template <int GP, int D>
+__device__ __forceinline__ void solver_cta(Topo tp, const Exchange& ex, IpmParams prm, Workspace* ws,
+                                           float* __restrict__ probs, Counter avail, int* status, int n_workers,
+                                           unsigned long long grid_timeout_ns, unsigned long long* __restrict__ trace,
+                                           int* smem) {
+  const int e = tp.e;
   const bool tracing = trace != nullptr && threadIdx.x == 0;
-  if (tracing && p == 0) trace[0] = global_timer_ns();
-  const RedirectTables tb = redirect_tables(smem, e);
-  int* hist = tb.total;  // this CTA's counts, later the rank-local totals
+  if (tracing) trace[0] = global_timer_ns();
   __shared__ uint32_t s_epoch;
-  __shared__ int s_ok;
-  __shared__ unsigned s_ticket;
   __shared__ ExchangeShared xs;
-
   if (threadIdx.x == 0) s_epoch = ld_acquire_gpu(&ws->epoch) + 1;
-  for (int i = threadIdx.x; i < e; i += kBlock) hist[i] = 0;
+  // The solver's inputs go to L2 and to this SM's L1 while the workers count (they were
+  // evicted if anything ran since the last step).
+  {
+    const int ranks = tp.n_group * tp.g;
+    for (int b = threadIdx.x * 128; b < e * 4; b += kBlock * 128)
+      asm volatile("prefetch.global.L1 [%0];" ::"l"(reinterpret_cast<const char*>(tp.log2slot) + b));
+    for (int b = threadIdx.x * 128; b < tp.g * tp.d * 4; b += kBlock * 128) {
+      asm volatile("prefetch.global.L1 [%0];" ::"l"(reinterpret_cast<const char*>(tp.r2o) + b));
+      asm volatile("prefetch.global.L1 [%0];" ::"l"(reinterpret_cast<const char*>(tp.o2r) + b));
+    }
+    if (prm.anchor != nullptr) {  // warm-start state: (4 D + 3) doubles per rank
+      for (int b = threadIdx.x * 128; b < ranks * (4 * D + 3) * 8; b += kBlock * 128)
+        asm volatile("prefetch.global.L1 [%0];" ::"l"(reinterpret_cast<const char*>(prm.anchor) + b));
+      if (threadIdx.x == 0) asm volatile("prefetch.global.L1 [%0];" ::"l"(prm.anchor_valid));
+    }
+  }
+  exchange_prepare(ex, &xs);
+  __shared__ int s_stop;
+  if (threadIdx.x == 0) s_stop = 0;
   __syncthreads();
   const uint32_t epoch = s_epoch;
   const int parity = epoch & 1;
   int* total_g = ws_total(ws, parity, e);
-
-  const long long begin = slice_begin(n, p, n_cta, kBlock), end = slice_begin(n, p + 1, n_cta, kBlock);
-  long long keep[kKeep];
-  if (p == 0) {
-    // Whichever CTA ends up solving will gather from these tables: pull them into L2 in the
-    // shadow of the counting phase (they were evicted if anything ran since the last step).
-    for (int i = threadIdx.x * 32; i < e; i += kBlock * 32) asm volatile("prefetch.global.L2 [%0];" ::"l"(tp.log2slot + i));
-    if (threadIdx.x == 0) {
-      asm volatile("prefetch.global.L2 [%0];" ::"l"(tp.r2o));
-      asm volatile("prefetch.global.L2 [%0];" ::"l"(tp.o2r));
+  int* vec = smem;  // rank-local, then group-wide totals
+  int* bundle = smem + e;
+  constexpr int NT = kBlock;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (warp == 1) {
+    if (lane == 0) {
+      if (!bounded_wait_ge<false>(&ws->arrive[parity], (uint32_t)n_workers, grid_timeout_ns)) {
+        atomicAdd(&status[kStTimeouts], 1);
+        raise_status(status, kErrGridTimeout, kPhCount, (int)ld_acquire_gpu(&ws->arrive[parity]));
+      }
+      *reinterpret_cast<volatile int*>(&s_stop) = 1;  // ends the rehearsal
+      if (trace != nullptr) trace[2] = global_timer_ns();
+      status[kStLpIters] = 0;
+      status[kStGapPpb] = 0;
+      // Every worker of this launch has read the launch number, so the bookkeeping for the next
+      // launch can be done here: its arrival counter starts at zero and it will see this launch
+      // as completed (launches of one engine are stream-ordered).
+      ws->arrive[parity ^ 1] = 0;
+      ws->epoch = epoch;
+      atomicAdd(&status[kStCalls], 1);
     }
-    if (prm.anchor != nullptr) {  // warm-start state: (4 D + 3) doubles per rank
-      const int n_bytes = tp.n_group * tp.g * (4 * D + 3) * 8;
-      for (int b = threadIdx.x * 128; b < n_bytes; b += kBlock * 128)
-        asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const char*>(prm.anchor) + b));
-      if (threadIdx.x == 1) asm volatile("prefetch.global.L2 [%0];" ::"l"(prm.anchor_valid));
+  } else if (warp == 0) {
+    if constexpr (GP != 0) {
+      // Rehearsal while the workers count: the warp that will solve runs the solver on made-up
+      // loads until the counts are in.  Whatever ran since the last step has evicted the
+      // solver's code from the caches, the instruction caches included, and one warp running
+      // two thousand straight-line instructions per iteration waits for every line of it; here
+      // it takes the first of those waits while it has nothing else to do.  Nothing it
+      // computes is kept.
+      const int li = lane % GP, g = tp.g;
+      double w[D], f[D];
+      int src[D], dst[D];
+#pragma unroll
+      for (int d = 0; d < D; ++d) {
+        const bool real = li < g && (d + 1) % g != 0;
+        w[d] = real ? 1.0 + 0.37 * li + 0.11 * d : 0.0;
+        src[d] = real ? (li + d + 1) % g : li;
+        dst[d] = real ? (li + g - (d + 1) % g) % g : li;
+      }
+      IpmParams rehearsal{3, 0.0};
+      rehearsal.stop = &s_stop;
+      ipm_solve_segment<GP, D>(li, w, li < g ? 3.0 + 0.2 * li : 0.0, src, dst, rehearsal, f);
     }
   }
+  team_sync<NT>();
+  // the workers' counts are in total_g: their atomics precede their arrivals
+  int* other = ws_total(ws, parity ^ 1, e);
+  const int first = threadIdx.x;
+  const int first_slot = first < e ? tp.log2slot[first] : 0;  // in flight while the exchange runs
+  for (int i = threadIdx.x; i < e; i += NT) {
+    vec[i] = __ldcg(&total_g[i]);
+    other[i] = 0;  // ready for the next launch
+  }
+  team_sync<NT>();
+  if (ex.n_ranks > 1) {
+    const unsigned miss = exchange_counts<NT>(ex, &xs, epoch, e, vec, status, trace != nullptr ? trace + 8 : nullptr);
+    if (miss) {
+      // Shares made from substituted statistics must not become the next warm start, and the
+      // saved iterate may no longer match the peers': this solve and the next one start cold.
+      if (prm.anchor_valid != nullptr)
+        for (int g = threadIdx.x; g < tp.n_group; g += NT) prm.anchor_valid[g] = 0;
+      prm.anchor = nullptr;
+      prm.anchor_valid = nullptr;
+      if (threadIdx.x == 0) {
+        atomicAdd(&status[kStTimeouts], 1);
+        raise_status(status, kErrPeerTimeout, kPhExchange, (int)miss);
+      }
+    }
+  }
+  if (tracing) trace[3] = global_timer_ns();
+  // group-wide counts -> per-rank bundle loads, and a copy for the host
+  int* glob = ws_global(ws, e);
+  const int n_bundle = tp.n_group * tp.g * (tp.d + 1);
+  for (int i = threadIdx.x; i < n_bundle; i += NT) bundle[i] = 0;
+  team_sync<NT>();
+  for (int i = threadIdx.x; i < e; i += NT) {
+    const int c = vec[i];
+    glob[i] = c;
+    const int slot = i == first ? first_slot : tp.log2slot[i];
+    if (c && LPLB_CHECKED(slot, n_bundle, status, kPhSolve)) atomicAdd(&bundle[slot], c);
+  }
+  team_sync<NT>();
+  if constexpr (GP == 0) {
+    solve_groups_block<D>(bundle, tp, 0, 1, prm, probs, avail, status, scratch_after(bundle, tp.n_group * tp.g, tp.d));
+  } else {
+    solve_groups<GP, D>(bundle, tp, 0, (NT / 32) * (32 / GP), prm, probs, avail, status);
+  }
+  __threadfence();
+  team_sync<NT>();
+  if (threadIdx.x == 0) st_release_gpu(&ws->lp_done, epoch);
+  if (tracing) trace[4] = global_timer_ns();
+}
+
+template <typename IdxT>
+__device__ __forceinline__ void worker_cta(const IdxT* __restrict__ idx, long long n, const Topo& tp, Workspace* ws,
+                                           const float* __restrict__ probs, int* status, IdxT* __restrict__ out,
+                                           int q, int n_workers, unsigned long long grid_timeout_ns,
+                                           unsigned long long* __restrict__ trace, int* smem) {
+  const int e = tp.e;
+  const bool tracing = trace != nullptr && threadIdx.x == 0 && q == 0;
+  const RedirectTables tb = redirect_tables(smem, e);
+  int* hist = tb.total;  // this CTA's counts, later the rank-local totals
+  __shared__ uint32_t s_epoch;
+  __shared__ int s_ok;
+  // Everything that does not depend on the launch number is issued before the first barrier:
+  // the launch number itself, this thread's indices, the static lookup tables.
+  if (threadIdx.x == 0) s_epoch = ld_acquire_gpu(&ws->epoch) + 1;
+  const long long begin = slice_begin(n, q, n_workers, kBlock), end = slice_begin(n, q + 1, n_workers, kBlock);
+  long long keep[kKeep];
   load_keep(idx, begin, end, keep);
-  // static lookup tables, fetched while the indices are on their way (quota[] holds the edge
-  // ids until the shares are known); the peers' buffer addresses likewise
   for (int i = threadIdx.x; i < e; i += kBlock) {
-    tb.quota[i] = tp.log2edge[i];
+    hist[i] = 0;
+    tb.quota[i] = tp.log2edge[i];  // the edge ids, until the shares are known
     tb.phys[i] = reinterpret_cast<const int2*>(tp.log2phy)[i];
   }
-  exchange_prepare(ex, &xs);
+  __syncthreads();
+  const uint32_t epoch = s_epoch;
+  int* total_g = ws_total(ws, epoch & 1, e);
   histogram_keep(idx, begin, end, e, hist, status, keep);
   __syncthreads();
   for (int i = threadIdx.x; i < e; i += kBlock) {
@@ -749,86 +874,13 @@ __global__ void __launch_bounds__(kBlock) fused_run_kernel(const IdxT* __restric
   }
   __threadfence();
   __syncthreads();
-  if (threadIdx.x == 0) s_ticket = atomicAdd(&ws->arrive, 1u);
-  if (tracing && p == 0) trace[1] = global_timer_ns();
-  __syncthreads();
-
-  bool leader = s_ticket == (unsigned)n_cta - 1;
-  if (leader_mode == 1) {
-    leader = p == 0;
-    if (leader) {
-      if (threadIdx.x == 0) {
-        s_ok = bounded_wait_ge<false>(&ws->arrive, (uint32_t)n_cta, grid_timeout_ns);
-        if (!s_ok) {
-          atomicAdd(&status[kStTimeouts], 1);
-          raise_status(status, kErrGridTimeout, kPhCount, (int)ld_acquire_gpu(&ws->arrive));
-        }
-      }
-      __syncthreads();
-    }
-  }
-  if (leader) {
-    // Every other CTA's counts are in total_g: their atomics precede their tickets.
-    __threadfence();
-    if (tracing) trace[2] = global_timer_ns();
-    if (threadIdx.x == 0) {
-      status[kStLpIters] = 0;
-      status[kStGapPpb] = 0;
-    }
-    int* vec = hist;  // this CTA's own counts are no longer needed: rank-local, then group-wide totals
-    int* other = ws_total(ws, parity ^ 1, e);
-    const int first = threadIdx.x;
-    const int first_slot = first < e ? tp.log2slot[first] : 0;  // in flight while the exchange runs
-    for (int i = threadIdx.x; i < e; i += kBlock) {
-      vec[i] = __ldcg(&total_g[i]);
-      other[i] = 0;  // ready for the next launch
-    }
-    __syncthreads();
-    if (ex.n_ranks > 1) {
-      const unsigned miss = exchange_counts(ex, &xs, epoch, e, vec, status, trace != nullptr ? trace + 8 : nullptr);
-      if (miss) {
-        // Shares made from substituted statistics must not become the next warm start, and the
-        // saved iterate may no longer match the peers': this solve and the next one start cold.
-        if (prm.anchor_valid != nullptr)
-          for (int g = threadIdx.x; g < tp.n_group; g += kBlock) prm.anchor_valid[g] = 0;
-        prm.anchor = nullptr;
-        prm.anchor_valid = nullptr;
-        if (threadIdx.x == 0) {
-          atomicAdd(&status[kStTimeouts], 1);
-          raise_status(status, kErrPeerTimeout, kPhExchange, (int)miss);
-        }
-      }
-    }
-    if (tracing) trace[3] = global_timer_ns();
-    // group-wide counts -> per-rank bundle loads, and a copy for the host
-    int* glob = ws_global(ws, e);
-    int* bundle = tb.rest;
-    const int n_bundle = tp.n_group * tp.g * (tp.d + 1);
-    for (int i = threadIdx.x; i < n_bundle; i += kBlock) bundle[i] = 0;
-    __syncthreads();
-    for (int i = threadIdx.x; i < e; i += kBlock) {
-      const int c = vec[i];
-      glob[i] = c;
-      const int slot = i == first ? first_slot : tp.log2slot[i];
-      if (c && LPLB_CHECKED(slot, n_bundle, status, kPhSolve)) atomicAdd(&bundle[slot], c);
-    }
-    __syncthreads();
-    if constexpr (GP == 0) {
-      solve_groups_block<D>(bundle, tp, 0, 1, prm, probs, avail, status, scratch_after(bundle, tp.n_group * tp.g, tp.d));
-    } else {
-      solve_groups<GP, D>(bundle, tp, 0, kWarps * (32 / GP), prm, probs, avail, status);
-    }
-    __threadfence();
-    __syncthreads();
-    if (threadIdx.x == 0) st_release_gpu(&ws->lp_done, epoch);
-    if (tracing) trace[4] = global_timer_ns();
-  }
-
   if (threadIdx.x == 0) {
+    atomicAdd(&ws->arrive[epoch & 1], 1u);
+    if (tracing) trace[1] = global_timer_ns();
     s_ok = bounded_wait_ge<false>(&ws->lp_done, epoch, grid_timeout_ns);
     if (!s_ok) {
       atomicAdd(&status[kStTimeouts], 1);
-      raise_status(status, kErrLpTimeout, kPhRedirect, p);
+      raise_status(status, kErrLpTimeout, kPhRedirect, q);
     }
   }
   __syncthreads();
@@ -841,19 +893,30 @@ __global__ void __launch_bounds__(kBlock) fused_run_kernel(const IdxT* __restric
   }
   __syncthreads();
   redirect_keep(idx, begin, end, e, tb.cur, tb.total, tb.quota, tb.phys, out, keep);
-
-  __syncthreads();
-  if (tracing && p == 0) trace[5] = global_timer_ns();
-  if (threadIdx.x == 0) {
-    __threadfence();
-    if (atomicAdd(&ws->exit_cnt, 1u) == (unsigned)n_cta - 1) {
-      ws->arrive = 0;
-      ws->exit_cnt = 0;
-      atomicAdd(&status[kStCalls], 1);
-      st_release_gpu(&ws->epoch, epoch);
-      if (trace != nullptr) trace[6] = global_timer_ns();
+  if (trace != nullptr) {  // tracing only: find the worker that leaves last
+    __syncthreads();
+    if (tracing) trace[5] = global_timer_ns();
+    if (threadIdx.x == 0) {
+      __threadfence();
+      if (atomicAdd(&ws->exit_cnt, 1u) == (unsigned)n_workers - 1) {
+        ws->exit_cnt = 0;
+        trace[6] = global_timer_ns();
+      }
     }
   }
+}
+
+// Grid = 1 solver CTA + (gridDim.x - 1) worker CTAs.
+template <int GP, int D, typename IdxT>
+__global__ void __launch_bounds__(kBlock) fused_run_kernel(const IdxT* __restrict__ idx, long long n, Topo tp,
+                                                           Exchange ex, IpmParams prm, Workspace* ws,
+                                                           float* __restrict__ probs, Counter avail, int* status,
+                                                           IdxT* __restrict__ out, unsigned long long grid_timeout_ns,
+                                                           unsigned long long* __restrict__ trace) {
+  extern __shared__ __align__(16) int smem[];
+  const int n_workers = (int)gridDim.x - 1;
+  if (blockIdx.x == 0) solver_cta<GP, D>(tp, ex, prm, ws, probs, avail, status, n_workers, grid_timeout_ns, trace, smem);
+  else worker_cta<IdxT>(idx, n, tp, ws, probs, status, out, (int)blockIdx.x - 1, n_workers, grid_timeout_ns, trace, smem);
 }
 
 }  // namespace lplb

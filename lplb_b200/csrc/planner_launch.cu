@@ -186,7 +186,6 @@ struct FusedLaunch {
   unsigned long long grid_timeout_ns;
   unsigned long long* trace;
   int cooperative;
-  int leader_mode;
   cudaStream_t stream;
   template <int GP, int D>
   cudaError_t operator()() {
@@ -194,7 +193,7 @@ struct FusedLaunch {
     const size_t smem = fused_smem(tp.e) + (GP == 0 ? block_smem(tp.n_group * tp.g, tp.g, tp.d) : bundle_smem(tp));
     cudaError_t err = allow_smem(kernel, smem);
     if (err != cudaSuccess) return err;
-    void* args[] = {&idx, &n, &tp, &ex, &prm, &ws, &probs, &avail, &status, &out, &grid_timeout_ns, &trace, &leader_mode};
+    void* args[] = {&idx, &n, &tp, &ex, &prm, &ws, &probs, &avail, &status, &out, &grid_timeout_ns, &trace};
     if (cooperative)
       return cudaLaunchCooperativeKernel(reinterpret_cast<void*>(kernel), dim3(n_cta), dim3(kBlock), args, smem,
                                          stream);
@@ -205,18 +204,18 @@ struct FusedLaunch {
 cudaError_t launch_fused(const void* idx, int idx_is64, long long n, const TopoDesc& topo, const ExchangeDesc& exd,
                          SolveParams prm, void* workspace, float* probs, void* avail, int avail_is64, int* status,
                          void* out, int n_cta, unsigned long long grid_timeout_ns, unsigned long long* trace,
-                         int cooperative, int leader_mode, cudaStream_t stream) {
-  if (!shape_ok(topo, true, prm.solver) || n_cta < 1 || exd.n_ranks > kMaxRanks) return cudaErrorInvalidValue;
+                         int cooperative, cudaStream_t stream) {
+  if (!shape_ok(topo, true, prm.solver) || n_cta < 2 || exd.n_ranks > kMaxRanks) return cudaErrorInvalidValue;
   Exchange ex{exd.recv, exd.n_ranks, exd.my_rank, exd.node_size, exd.timeout_ns};
   if (idx_is64) {
     FusedLaunch<int64_t> l{static_cast<const int64_t*>(idx), n, make_topo(topo), ex, make_params(prm),
                            static_cast<Workspace*>(workspace), probs, Counter{avail, avail_is64}, status,
-                           static_cast<int64_t*>(out), n_cta, grid_timeout_ns, trace, cooperative, leader_mode, stream};
+                           static_cast<int64_t*>(out), n_cta, grid_timeout_ns, trace, cooperative, stream};
     return dispatch_shape(topo.g, topo.d, prm.solver, l);
   }
   FusedLaunch<int32_t> l{static_cast<const int32_t*>(idx), n, make_topo(topo), ex, make_params(prm),
                          static_cast<Workspace*>(workspace), probs, Counter{avail, avail_is64}, status,
-                         static_cast<int32_t*>(out), n_cta, grid_timeout_ns, trace, cooperative, leader_mode, stream};
+                         static_cast<int32_t*>(out), n_cta, grid_timeout_ns, trace, cooperative, stream};
   return dispatch_shape(topo.g, topo.d, prm.solver, l);
 }
 
@@ -253,15 +252,5 @@ int max_fused_ctas(const TopoDesc& topo, int solver, int idx_is64) {
   if (dispatch_shape(topo.g, topo.d, solver, q) != cudaSuccess) return 0;
   return result;
 }
-
-#ifdef LPLB_BLK_PROFILE
-void blk_profile_read(unsigned long long* out16, int reset) {
-  cudaMemcpyFromSymbol(out16, g_blk_prof, sizeof(unsigned long long) * 16);
-  if (reset) {
-    unsigned long long zero[16] = {};
-    cudaMemcpyToSymbol(g_blk_prof, zero, sizeof(zero));
-  }
-}
-#endif
 
 }  // namespace lplb

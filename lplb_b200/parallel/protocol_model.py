@@ -3,8 +3,12 @@
 The kernel protocol (``exchange_counts`` in ``csrc/planner_kernels.cuh``): in launch number
 ``n`` (the epoch) every rank stores, for each element, the word ``(n << 32) | count`` into
 slot ``[n & 1][my_rank]`` of every rank's receive buffer, then polls its own buffer until
-every word of parity ``n & 1`` carries tag ``n`` or a time budget runs out, then sums.  A
-rank whose words did not arrive in time is reported and replaced by the reader's own counts.
+every word of parity ``n & 1`` carries tag ``n`` or a time budget runs out, summing the words
+as they arrive (the sum replaces the rank's own vector in place).  A rank whose words did not
+arrive in time is reported and replaced by the reader's own counts, which the reader takes
+from its own slot of its receive buffer (it pushes to itself like to any peer).  The kernel
+stores two adjacent words with one 16-byte store when the vector length is even; each half
+carries its own tag, so the model's unit of delivery stays the single word.
 With a node size the exchange runs in two levels, each with its own slots
 ``[n & 1][level][my_rank]``: first among the ranks of a node, then the node sums among the
 ranks that hold the same position in every node (``two_level_step``).  Counts use 31 bits;
@@ -99,8 +103,13 @@ class Rank:
         miss = sum(1 << r for r in peers if not ok[r])
         # a vector that arrived but carries the degraded mark is used as it is and reported
         miss |= sum(1 << r for r in peers if ok[r] and buf[r][0] & 0x80000000)
+        # the substitute for an absent rank is this rank's own vector as it sits in its own slot
+        own = [
+            (buf[self.rank][e] & 0x7FFFFFFF) if (buf[self.rank][e] >> 32) == self.epoch else self.mine[e]
+            for e in range(self.n_elems)
+        ]
         sums = [
-            sum((buf[src][e] & 0x7FFFFFFF) if ok[src] else self.mine[e] for src in peers)
+            sum((buf[src][e] & 0x7FFFFFFF) if ok[src] else own[e] for src in peers)
             for e in range(self.n_elems)
         ]
         return sums, miss

@@ -187,8 +187,6 @@ class Planner:
             )
             if solver != "auto":
                 self._engine.set_solver(solver)
-            if os.environ.get("LPLB_B200_LEADER"):
-                self._engine.set_leader_mode(1 if os.environ["LPLB_B200_LEADER"] == "cta0" else 0)
             self._native_solver = bool(self._engine.has_native_solver())
             if not self._native_solver:
                 log.warning(
@@ -404,6 +402,9 @@ class Planner:
         """Logical expert ids ``[-1, E)`` in, physical expert ids ``[-1, P)`` out, same shape
         (reference ``lplb/planner.py:245-266``).
 
+        ``n_sms`` CTAs are launched (default: one per SM, never fewer than two): one of them
+        exchanges the statistics and solves the LPs, the others count and rewrite the indices.
+
         ``idx`` normally lives on the planner's GPU.  It may instead be a *pinned host* tensor:
         the kernel then reads it over PCIe itself (no separate host-to-device copy), and the
         result is written to ``out``, which may be a pinned host tensor as well (no separate
@@ -535,9 +536,10 @@ class Planner:
     def phase_times_us(self) -> dict[str, float] | None:
         """Phase durations of the last fused ``run`` in microseconds; synchronises.
 
-        ``count`` and ``redirect`` are CTA 0's; ``last_count`` is the wait until the last CTA's
-        counts were in; ``exchange``, ``solve`` belong to the CTA that took the last arrival
-        ticket.  With a peer exchange the ``exchange`` phase is split further, measured from its
+        ``count`` is the time until the first worker CTA had counted its slice, ``last_count``
+        the further wait until all counts were in; ``exchange`` and ``solve`` belong to the solver
+        CTA; ``redirect`` ends when the first worker has rewritten its slice, ``drain`` when the
+        last one has.  With a peer exchange the ``exchange`` phase is split further, measured from its
         start: ``xchg_pushed`` (this rank's stores to all peers issued), ``xchg_first_peer`` and
         ``xchg_last_peer`` (first and last word of another rank seen), and ``xchg_last_peer_rank``;
         what lies between ``xchg_pushed`` and ``xchg_last_peer`` is wire time plus waiting for the
