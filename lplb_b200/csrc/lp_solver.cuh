@@ -393,6 +393,7 @@ __device__ __forceinline__ IpmOutcome ipm_solve_segment(int li, const double (&w
     // Every segment of the warp has to leave the loop together.
     if (__all_sync(0xffffffffu, done) || it == prm.max_iters) break;
     if (!done) ++iters;
+    if (told_to_stop()) break;
 
     // ---- normal matrix row -----------------------------------------------------------
     double inv_f[D], inv_v[D], theta[D], cw[D];
@@ -468,6 +469,10 @@ __device__ __forceinline__ IpmOutcome ipm_solve_segment(int li, const double (&w
         double b2 = pass == 0 ? 1.0 : 0.0;
         ldl_solve_rows<GP, 2>(row, li, a, b2);
         if (pass == 0) border = b2;
+      }
+      if (told_to_stop()) {
+        halted = true;
+        break;
       }
       if (pass == 0) inv_border_sum = fast_rcp(seg_sum<GP>(border));
       dt = (seg_sum<GP>(a) - r_t) * inv_border_sum;
