@@ -30,6 +30,20 @@ def test_bench_defaults_follow_the_contract():
     assert bench.N_LOGICAL == 256 and bench.EP_SIZE == 8 and bench.TOKENS_PER_RANK == 4096 and bench.TOP_K == 8
 
 
+def test_a_bias_redraw_falls_inside_the_timed_steps():
+    sys.path.insert(0, ROOT)
+    import bench
+
+    for steps, warmup in ((20, 5), (200, 20), (3, 3), (40, 5), (20, 60)):
+        first = bench.first_step(steps, warmup)
+        assert first >= 0
+        timed = range(first + warmup, first + warmup + steps)
+        redraws = [s for s in timed if s % bench.BIAS_PERIOD == 0]
+        assert redraws, (steps, warmup, first)
+        # not at the very first timed step: the steps before it run on the old distribution
+        assert redraws[0] > timed[0] or steps < 2
+
+
 def test_clock_sampler_reads_a_fake_nvml(monkeypatch):
     """The sampler only reads: clock, power and event reasons, through whatever NVML binding is importable."""
     import sys
