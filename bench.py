@@ -459,6 +459,13 @@ def run_reference(argv: list[str]) -> dict:
     ref_dir = os.path.join(ROOT, "baseline", "_ref", "lplb")
     if not os.path.isdir(ref_dir):
         return {"impl": "reference", "unavailable": "baseline/_ref is not installed (offline pip install of the reference checkout was not done)"}
+    if not os.path.isdir(os.path.join(ref_dir, "resources", "mathdx")):
+        # The one blocker that cannot be fixed offline; nothing of the reference is run without it
+        # (its run-time compile of minilp.cu can only fail, and did so with a crash of the child
+        # process instead of an error message on a GPU box).
+        return {"impl": "reference", "unavailable": "lplb/resources/mathdx is absent: all four kernels sit in minilp.cu, "
+                "which includes cublasdx.hpp and cusolverdx.hpp (MathDx 25.06.0, fetched by download-mathdx.sh from the "
+                "network); no copy of MathDx exists on this machine, so the reference's kernels cannot be compiled"}
     env = dict(os.environ)
     env.setdefault("LPLB_CACHE_PATH", os.path.join(ROOT, "baseline", "_ref", "_jit_cache"))
     code = f"ROOT = {ROOT!r}\nARGV = {argv!r}\nJITLINK = {find_jitlink()!r}\n" + REFERENCE_DRIVER
