@@ -414,7 +414,13 @@ class Planner:
         if n_sms is None:
             n_sms = self._default_sms()
         with self._nvtx("lplb_b200.planner.run"):
-            if self._engine is not None and self._native_solver and self.comm != "nccl":
+            # One launch, unless the statistics travel through torch.distributed, or several
+            # groups need the thread-block solver: inside the one launch a single CTA would solve
+            # them one after the other, the stand-alone solve kernel gives every group a CTA.
+            fused = self._engine is not None and self._native_solver and self.comm != "nccl"
+            if fused and self.n_group > 1 and self._engine.solver() == "block":
+                fused = False
+            if fused:
                 if not idx.is_cuda and out is None:
                     key = (tuple(idx.shape), idx.dtype)
                     if self._host_out is None or self._host_out[0] != key:

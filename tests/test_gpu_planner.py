@@ -482,6 +482,22 @@ def test_block_and_warp_solver_agree():
         assert float((warp.last_probs - block.last_probs).abs().max()) < 2e-4
 
 
+def test_several_wide_groups_are_solved_side_by_side():
+    # hypercube with ep_size 64: four LP groups of 16 ranks.  `run` leaves the single launch so
+    # that every group gets a CTA of its own; result and status are as for any other call.
+    planner = _planner(topology.hypercube(), 256, 64, 2)
+    assert planner._engine.solver() == "block" and planner.n_group == 4
+    gen = torch.Generator("cuda").manual_seed(8)
+    idx = (torch.randn(4096, 256, device="cuda", generator=gen) + torch.randn(256, device="cuda", generator=gen)).topk(8, dim=-1).indices
+    avail = torch.zeros(1, dtype=torch.int32, device="cuda")
+    out = planner.run(idx, avail)
+    assert int(avail) == 4
+    counts, _ = planner.count_workload(idx, _sms())
+    probs, _ = planner.solve_probs(counts, torch.zeros(1, dtype=torch.int32, device="cuda"))
+    _check_redirect(planner, idx, out, probs)
+    assert planner.check_status().ok
+
+
 def test_odd_number_of_experts_keeps_the_tables_aligned():
     # 9 ranks x 3 logical experts = 27: the int2 table of the redirect phase must not depend on
     # the parity of the expert count
