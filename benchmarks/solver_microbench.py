@@ -53,8 +53,9 @@ def main():
     n_batches = -(-args.instances // batch)
     r2o = cube()
 
-    big = Planner(r2o, (128 + 16) * batch, 128 * batch, 8 * batch, device=dev, tol=args.tol)
-    one = Planner(r2o, 128 + 16, 128, 8, device=dev, tol=args.tol)
+    # unrelated instances follow one another, so every solve starts from scratch
+    big = Planner(r2o, (128 + 16) * batch, 128 * batch, 8 * batch, device=dev, tol=args.tol, warm_start=False)
+    one = Planner(r2o, 128 + 16, 128, 8, device=dev, tol=args.tol, warm_start=False)
     avail = torch.zeros(1, dtype=torch.int32, device=dev)
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
 

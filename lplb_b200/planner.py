@@ -168,6 +168,7 @@ class Planner:
         self._anchor: dict | None = None  # CPU path only; the engine keeps its own on the device
         self.exchange_node_size = int(exchange_node_size)
         self._host_out: tuple | None = None
+        self._staged_probs: torch.Tensor | None = None
         self._status_mirror: list | None = None
         self._nvtx_on = self.device.type == "cuda" and os.environ.get("LPLB_B200_NVTX") == "1"
 
@@ -426,11 +427,13 @@ class Planner:
                     if self._host_out is None or self._host_out[0] != key:
                         self._host_out = (key, torch.empty(idx.shape, dtype=idx.dtype).pin_memory())
                     out = self._host_out[1]
+                self._staged_probs = None
                 return self._engine.run_fused(idx.contiguous(), avail_counter, int(n_sms), self.comm == "p2p", out)
             if not idx.is_cuda and self._engine is not None:
                 idx = idx.to(self.device, non_blocking=True)
             local, by_sm = self.count_workload(idx, n_sms)
             probs, _ = self.solve_probs(local, avail_counter)
+            self._staged_probs = probs
             res = self.weighted_select_target(idx, probs, by_sm, n_sms)
             if out is not None:
                 out.copy_(res, non_blocking=True)
@@ -447,8 +450,10 @@ class Planner:
 
     @property
     def last_probs(self) -> torch.Tensor | None:
-        """Shares ``[NG, G, D]`` computed by the most recent fused ``run``."""
-        return None if self._engine is None else self._engine.last_probs()
+        """Shares ``[NG, G, D]`` computed by the most recent ``run``."""
+        if self._staged_probs is not None or self._engine is None:
+            return self._staged_probs
+        return self._engine.last_probs()
 
     # ------------------------------------------------------------------ observability
     @staticmethod

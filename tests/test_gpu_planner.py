@@ -475,10 +475,15 @@ def test_block_and_warp_solver_agree():
         assert int(a1) == int(a2) == n_group and torch.equal(n1, n2)
         assert float((p1 - p2).abs().max()) < 2e-4  # same method, different elimination order
         assert warp.check_status()["lp_iters"] == block.check_status()["lp_iters"]
-        # and inside the fused kernel
+        # and inside the fused kernel (`run` would give several block-solver groups a launch of
+        # their own, so the engine is called directly)
         idx = torch.randint(-1, e, (3000, 4), device="cuda")
-        o1, o2 = warp.run(idx, a1), block.run(idx, a2)
-        _check_redirect(block, idx, o2, block.last_probs.clone())
+        warp.run(idx, a1)
+        o2 = block._engine.run_fused(idx, a2, _sms(), False, None)
+        _check_redirect(block, idx, o2, block._engine.last_probs().clone())
+        assert float((warp.last_probs - block._engine.last_probs()).abs().max()) < 2e-4
+        o3 = block.run(idx, a2)
+        _check_redirect(block, idx, o3, block.last_probs.clone())
         assert float((warp.last_probs - block.last_probs).abs().max()) < 2e-4
 
 
