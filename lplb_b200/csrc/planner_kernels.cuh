@@ -404,22 +404,26 @@ __device__ __forceinline__ void normalise_counts(const int* __restrict__ workloa
   __syncthreads();
 }
 
-// Stand-alone solve kernel, warp solver: one CTA per `kWarps * 32/GP` groups.  `workload` is
+// Stand-alone solve kernel, warp solver: one CTA per `solver_warps * 32/GP` groups.  `workload` is
 // int32[E], already summed over ranks by the caller.
 template <int GP, int D>
 __global__ void __launch_bounds__(kBlock) solve_kernel(const int* __restrict__ workload, Topo tp, IpmParams prm,
                                                        float* __restrict__ probs, float* __restrict__ normalised,
-                                                       Counter avail, int* status) {
+                                                       Counter avail, int* status, int solver_warps) {
   if (blockIdx.x == 0) {
     if (threadIdx.x == 0) status[kStLpIters] = status[kStGapPpb] = 0;
     normalise_counts(workload, tp.e, normalised);
   }
   extern __shared__ __align__(16) int smem[];
   int* bundle = smem;
-  constexpr int kPerCta = kWarps * (32 / GP);
-  bundle_sums(workload, tp, bundle, min(tp.n_group, (int)blockIdx.x * kPerCta) * tp.g,
-              min(tp.n_group, ((int)blockIdx.x + 1) * kPerCta) * tp.g, status);
-  solve_groups<GP, D>(bundle, tp, blockIdx.x * kPerCta, gridDim.x * kPerCta, prm, probs, avail, status);
+  // Only the first `solver_warps` warps solve (the host spreads the groups over as many SMs as
+  // it can: a warp that has an SM's double-precision pipes to itself is the fastest); all
+  // warps help with the bundle sums.
+  const int per_cta = solver_warps * (32 / GP);
+  bundle_sums(workload, tp, bundle, min(tp.n_group, (int)blockIdx.x * per_cta) * tp.g,
+              min(tp.n_group, ((int)blockIdx.x + 1) * per_cta) * tp.g, status);
+  if ((int)(threadIdx.x >> 5) < solver_warps)
+    solve_groups<GP, D>(bundle, tp, blockIdx.x * per_cta, gridDim.x * per_cta, prm, probs, avail, status);
 }
 
 // Stand-alone solve kernel, thread-block solver: one CTA per group (the reference launches

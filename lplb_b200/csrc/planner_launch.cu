@@ -121,12 +121,18 @@ struct SolveLaunch {
       if (err != cudaSuccess) return err;
       solve_block_kernel<D><<<tp.n_group, kBlock, smem, stream>>>(workload, tp, prm, probs, normalised, avail, status);
     } else {
-      constexpr int per_cta = kWarps * (32 / GP);
+      // As few solving warps per CTA as still fit the groups on one wave of CTAs.
+      int dev = 0, sms = 1;
+      cudaError_t err = cudaGetDevice(&dev);
+      if (err == cudaSuccess) err = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+      if (err != cudaSuccess) return err;
+      int warps = 1;
+      while (warps < kWarps && (tp.n_group + warps * (32 / GP) - 1) / (warps * (32 / GP)) > sms) warps *= 2;
+      const int per_cta = warps * (32 / GP);
       const int grid = (tp.n_group + per_cta - 1) / per_cta;
       const size_t smem = bundle_smem(tp);
-      cudaError_t err = allow_smem(solve_kernel<GP, D>, smem);
-      if (err != cudaSuccess) return err;
-      solve_kernel<GP, D><<<grid, kBlock, smem, stream>>>(workload, tp, prm, probs, normalised, avail, status);
+      if ((err = allow_smem(solve_kernel<GP, D>, smem)) != cudaSuccess) return err;
+      solve_kernel<GP, D><<<grid, kBlock, smem, stream>>>(workload, tp, prm, probs, normalised, avail, status, warps);
     }
     return cudaGetLastError();
   }

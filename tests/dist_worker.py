@@ -13,7 +13,7 @@ import torch.distributed as dist
 
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
-from lplb_b200 import Planner, cube, lp  # noqa: E402
+from lplb_b200 import Planner, cube, hypercube, lp  # noqa: E402
 
 
 def main():
@@ -68,8 +68,13 @@ def main():
     # 2a. four LP groups (ep_size 32 on the Cube) and four redundant experts per rank (two per
     # topology slot), statistics from the `world` real ranks over the in-kernel exchange
     keep_alive = []
-    for name, ep_size, n_red in (("four groups", 32, 2), ("two experts per slot", 8, 4)):
-        multi = Planner(cube(), 256 + n_red * ep_size, 256, ep_size, group, device=dev, comm="p2p", warm_start=False)
+    # and two groups of 16 ranks (thread-block solver): `run` gives each group a CTA of its own,
+    # so it counts, exchanges (stand-alone exchange kernel over the same peer slots), solves and
+    # redirects in separate launches
+    for name, r2o, ep_size, n_red in (("four groups", cube(), 32, 2), ("two experts per slot", cube(), 8, 4),
+                                      ("two wide groups", hypercube(), 32, 2)):
+        multi = Planner(r2o, 256 + n_red * ep_size, 256, ep_size, group, device=dev, comm="p2p", warm_start=False)
+        one_launch = not (multi.n_group > 1 and multi._engine.solver() == "block")
         for step in range(4):
             logits = torch.randn(2048, 256, device=dev, generator=gen) + bias
             idx = logits.bfloat16().topk(8, dim=-1).indices
@@ -80,8 +85,9 @@ def main():
             avail = torch.zeros(1, dtype=torch.int32, device=dev)
             multi.run(idx, avail, 148 if step % 2 else 20)
             assert int(avail) == multi.n_group, name
-            ws = multi._engine.workspace()
-            assert torch.equal(ws[8 + 2 * 256 : 8 + 3 * 256].long(), counts), f"rank {rank}: {name}: global counts differ"
+            if one_launch:
+                ws = multi._engine.workspace()
+                assert torch.equal(ws[8 + 2 * 256 : 8 + 3 * 256].long(), counts), f"rank {rank}: {name}: global counts differ"
             probs = multi.last_probs.clone()
             gathered = [torch.empty_like(probs) for _ in range(world)]
             dist.all_gather(gathered, probs, group=group)
