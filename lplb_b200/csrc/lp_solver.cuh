@@ -60,26 +60,30 @@ struct IpmOutcome {
   double gap;
 };
 
+// Mask of the first n lanes of a warp.
+__host__ __device__ constexpr unsigned first_lanes(int n) { return n >= 32 ? 0xffffffffu : (1u << (n & 31)) - 1u; }
+
+// `lanes` in all of these: the lanes that execute the call (whole segments).
 template <int GP>
-__device__ __forceinline__ double seg_shfl(double v, int src) {
-  return __shfl_sync(0xffffffffu, v, src, GP);
+__device__ __forceinline__ double seg_shfl(unsigned lanes, double v, int src) {
+  return __shfl_sync(lanes, v, src, GP);
 }
 template <int GP>
-__device__ __forceinline__ double seg_sum(double v) {
+__device__ __forceinline__ double seg_sum(unsigned lanes, double v) {
 #pragma unroll
-  for (int o = GP / 2; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o, GP);
+  for (int o = GP / 2; o > 0; o >>= 1) v += __shfl_xor_sync(lanes, v, o, GP);
   return v;
 }
 template <int GP>
-__device__ __forceinline__ double seg_max(double v) {
+__device__ __forceinline__ double seg_max(unsigned lanes, double v) {
 #pragma unroll
-  for (int o = GP / 2; o > 0; o >>= 1) v = fmax(v, __shfl_xor_sync(0xffffffffu, v, o, GP));
+  for (int o = GP / 2; o > 0; o >>= 1) v = fmax(v, __shfl_xor_sync(lanes, v, o, GP));
   return v;
 }
 template <int GP>
-__device__ __forceinline__ float seg_minf(float v) {
+__device__ __forceinline__ float seg_minf(unsigned lanes, float v) {
 #pragma unroll
-  for (int o = GP / 2; o > 0; o >>= 1) v = fminf(v, __shfl_xor_sync(0xffffffffu, v, o, GP));
+  for (int o = GP / 2; o > 0; o >>= 1) v = fminf(v, __shfl_xor_sync(lanes, v, o, GP));
   return v;
 }
 
@@ -114,10 +118,10 @@ __device__ __forceinline__ double fast_rcp(double x) {
 // unrolled code of an iteration is close to the instruction cache's size at GP = 32, where
 // the measured time moves by +-25 % with the code's size and layout.
 template <int GP>
-__device__ __forceinline__ void ldl_factor_rows(double (&row)[GP], int li) {
+__device__ __forceinline__ void ldl_factor_rows(unsigned lanes, double (&row)[GP], int li) {
 #pragma unroll
   for (int j = 0; j < GP; ++j) {
-    double piv = seg_shfl<GP>(row[j], j);
+    double piv = seg_shfl<GP>(lanes, row[j], j);
     if (!(piv > 1e-300) || !(piv < 1e300)) piv = 1e300;
     const double dinv = fast_rcp(piv);
     const double lij = li > j ? row[j] * dinv : 0.0;  // L[i][j] on lanes below the pivot, else 0
@@ -126,7 +130,7 @@ __device__ __forceinline__ void ldl_factor_rows(double (&row)[GP], int li) {
     const double scale = li == j ? dinv : 1.0;
 #pragma unroll
     for (int k = j + 1; k < GP; ++k) {
-      const double u = seg_shfl<GP>(row[k], j);  // unscaled N[j][k] = N[k][j]
+      const double u = seg_shfl<GP>(lanes, row[k], j);  // unscaled N[j][k] = N[k][j]
       row[k] = fma(-lij, u, row[k]) * scale;
     }
     row[j] = li > j ? lij : (li == j ? dinv : row[j]);
@@ -135,12 +139,12 @@ __device__ __forceinline__ void ldl_factor_rows(double (&row)[GP], int li) {
 
 // Solve L D L^T x = g for NRHS (1 or 2) right-hand sides held one element per lane.
 template <int GP, int NRHS>
-__device__ __forceinline__ void ldl_solve_rows(const double (&row)[GP], int li, double& g0, double& g1) {
+__device__ __forceinline__ void ldl_solve_rows(unsigned lanes, const double (&row)[GP], int li, double& g0, double& g1) {
 #pragma unroll
   for (int j = 0; j < GP; ++j) {
     const double l = li > j ? row[j] : 0.0;
-    g0 = fma(-l, seg_shfl<GP>(g0, j), g0);
-    if constexpr (NRHS == 2) g1 = fma(-l, seg_shfl<GP>(g1, j), g1);
+    g0 = fma(-l, seg_shfl<GP>(lanes, g0, j), g0);
+    if constexpr (NRHS == 2) g1 = fma(-l, seg_shfl<GP>(lanes, g1, j), g1);
   }
   {
     double dinv = row[0];
@@ -152,8 +156,8 @@ __device__ __forceinline__ void ldl_solve_rows(const double (&row)[GP], int li, 
 #pragma unroll
   for (int j = GP - 1; j >= 0; --j) {
     const double l = li < j ? row[j] : 0.0;
-    g0 = fma(-l, seg_shfl<GP>(g0, j), g0);
-    if constexpr (NRHS == 2) g1 = fma(-l, seg_shfl<GP>(g1, j), g1);
+    g0 = fma(-l, seg_shfl<GP>(lanes, g0, j), g0);
+    if constexpr (NRHS == 2) g1 = fma(-l, seg_shfl<GP>(lanes, g1, j), g1);
   }
 }
 
@@ -167,11 +171,11 @@ struct Ldl8 {
   __device__ __forceinline__ static constexpr int at(int i, int k) { return i * (i + 1) / 2 + k; }
 };
 
-__device__ __forceinline__ void ldl8_factor(const double (&row)[8], Ldl8& m) {
+__device__ __forceinline__ void ldl8_factor(unsigned lanes, const double (&row)[8], Ldl8& m) {
 #pragma unroll
   for (int i = 0; i < 8; ++i)
 #pragma unroll
-    for (int k = 0; k <= i; ++k) m.a[Ldl8::at(i, k)] = seg_shfl<8>(row[k], i);
+    for (int k = 0; k <= i; ++k) m.a[Ldl8::at(i, k)] = seg_shfl<8>(lanes, row[k], i);
 #pragma unroll
   for (int j = 0; j < 8; ++j) {
     double piv = m.a[Ldl8::at(j, j)];
@@ -188,10 +192,10 @@ __device__ __forceinline__ void ldl8_factor(const double (&row)[8], Ldl8& m) {
   }
 }
 
-__device__ __forceinline__ double ldl8_solve(const Ldl8& m, int li, double g) {
+__device__ __forceinline__ double ldl8_solve(unsigned lanes, const Ldl8& m, int li, double g) {
   double b[8];
 #pragma unroll
-  for (int k = 0; k < 8; ++k) b[k] = seg_shfl<8>(g, k);
+  for (int k = 0; k < 8; ++k) b[k] = seg_shfl<8>(lanes, g, k);
 #pragma unroll
   for (int j = 0; j < 8; ++j)
 #pragma unroll
@@ -208,7 +212,8 @@ __device__ __forceinline__ double ldl8_solve(const Ldl8& m, int li, double g) {
   return x;
 }
 
-// All 32 lanes must call this together.  `li` is the lane's index inside its segment.
+// The lanes in `lanes` (whole segments of GP lanes) call this together, no others.  `li` is the
+// lane's index inside its segment.
 // Always inlined into its caller: left to the compiler, the decision changed from build to build
 // with unrelated edits elsewhere in the translation unit, and a solve ran 2 to 4 us slower
 // whenever the function ended up out of line.
@@ -224,7 +229,7 @@ template <int GP, int D>
 __device__ __forceinline__ IpmOutcome ipm_solve_segment(int li, const double (&w_in)[D], double fixed, const int (&src_in)[D],
                                                         const int (&dst_in)[D], const IpmParams prm,
                                                         double (&f_out)[D], double* anchor = nullptr,
-                                                        int* anchor_valid = nullptr) {
+                                                        int* anchor_valid = nullptr, const unsigned lanes = 0xffffffffu) {
   constexpr double kEta = 0.995;
   constexpr int kComp = GP + 2 * GP * D;
   // Private copies: when this function is not inlined the caller's arrays live in local memory,
@@ -240,7 +245,7 @@ __device__ __forceinline__ IpmOutcome ipm_solve_segment(int li, const double (&w
   double mine = fixed;
 #pragma unroll
   for (int d = 0; d < D; ++d) mine += w_in[d];
-  const double total = seg_sum<GP>(mine);
+  const double total = seg_sum<GP>(lanes, mine);
   IpmOutcome out{0, true, true, 0.0};
   // A segment with no load at all (also: a segment past the last group) must still walk
   // through every shuffle below with the rest of the warp, so it is not returned early:
@@ -251,7 +256,7 @@ __device__ __forceinline__ IpmOutcome ipm_solve_segment(int li, const double (&w
 #pragma unroll
   for (int d = 0; d < D; ++d) {
     w[d] = w_in[d] * inv_scale;
-    base += seg_shfl<GP>(w[d], src[d]);
+    base += seg_shfl<GP>(lanes, w[d], src[d]);
   }
   // A self edge (origin == holder; also every padding lane) moves no load: its column
   // of M is zero.  Its load is already part of `base`, so drop the weight.
@@ -264,7 +269,7 @@ __device__ __forceinline__ IpmOutcome ipm_solve_segment(int li, const double (&w
 #pragma unroll
     for (int d = 0; d < D; ++d) {
       const double wx = w[d] * x[d];
-      acc += wx - seg_shfl<GP>(wx, src[d]);
+      acc += wx - seg_shfl<GP>(lanes, wx, src[d]);
     }
     return acc;
   };
@@ -274,12 +279,12 @@ __device__ __forceinline__ IpmOutcome ipm_solve_segment(int li, const double (&w
 #pragma unroll
   for (int d = 0; d < D; ++d) f[d] = v[d] = 0.5;
   double load = base + m_times(f);
-  const double lmax = seg_max<GP>(load), lmin = -seg_max<GP>(-load);
+  const double lmax = seg_max<GP>(lanes, load), lmin = -seg_max<GP>(lanes, -load);
   double t = lmax + 0.5 * (lmax - lmin) + 0.05;
   double s = t - load;
   double y = 1.0 / GP;
   {
-    const double mu0 = seg_sum<GP>(s * y) / GP;
+    const double mu0 = seg_sum<GP>(lanes, s * y) / GP;
 #pragma unroll
     for (int d = 0; d < D; ++d) z[d] = q[d] = 2.0 * mu0;
   }
@@ -318,9 +323,9 @@ __device__ __forceinline__ IpmOutcome ipm_solve_segment(int li, const double (&w
     const double mfa = m_times(fa);  // shuffles inside: every lane takes part, with or without a slot
     const double rp = have ? fabs(ta - base - mfa - sa) : 0.0;
     // every reduction below is executed by all 32 lanes, whatever their segment decides
-    const bool seg_has = seg_max<GP>(have ? 1.0 : 0.0) > 0.0;
-    const double rp_max = seg_max<GP>(rp);
-    const double t_anchor = seg_max<GP>(have ? ta : -1e300);
+    const bool seg_has = seg_max<GP>(lanes, have ? 1.0 : 0.0) > 0.0;
+    const double rp_max = seg_max<GP>(lanes, rp);
+    const double t_anchor = seg_max<GP>(lanes, have ? ta : -1e300);
     const bool fits = seg_has && !empty && rp_max <= prm.guard;
     if (fits && have) {
 #pragma unroll
@@ -345,7 +350,7 @@ __device__ __forceinline__ IpmOutcome ipm_solve_segment(int li, const double (&w
   double gap = 1e300, gap_scale = 1.0;
 
   // one shared-memory read for the whole warp, so every lane takes the same way out
-  auto told_to_stop = [&]() -> bool { return prm.stop != nullptr && __any_sync(0xffffffffu, *prm.stop != 0); };
+  auto told_to_stop = [&]() -> bool { return prm.stop != nullptr && __any_sync(lanes, *prm.stop != 0); };
   bool halted = false;
 
   for (int it = 0; it <= prm.max_iters; ++it) {
@@ -358,17 +363,17 @@ __device__ __forceinline__ IpmOutcome ipm_solve_segment(int li, const double (&w
 #pragma unroll
     for (int d = 0; d < D; ++d) {
       r_u[d] = 1.0 - f[d] - v[d];
-      r_d[d] = z[d] - q[d] - w[d] * (y - seg_shfl<GP>(y, dst[d]));
+      r_d[d] = z[d] - q[d] - w[d] * (y - seg_shfl<GP>(lanes, y, dst[d]));
       comp += z[d] * f[d] + q[d] * v[d];
       dual_part -= q[d];
       neg_rd += fmin(r_d[d], 0.0);
       worst_u = fmax(worst_u, fabs(r_u[d]));
     }
-    const double mu = seg_sum<GP>(comp) / kComp;
-    const double r_t = 1.0 - seg_sum<GP>(y);
-    const double primal = seg_max<GP>(base + mf);
-    const double dual = seg_sum<GP>(dual_part + neg_rd);
-    const double infeas = fmax(seg_max<GP>(worst_u), fabs(r_t));
+    const double mu = seg_sum<GP>(lanes, comp) / kComp;
+    const double r_t = 1.0 - seg_sum<GP>(lanes, y);
+    const double primal = seg_max<GP>(lanes, base + mf);
+    const double dual = seg_sum<GP>(lanes, dual_part + neg_rd);
+    const double infeas = fmax(seg_max<GP>(lanes, worst_u), fabs(r_t));
     if (!done) {
       gap = primal - dual;  // absolute here, made relative once at the end
       gap_scale = fabs(primal);
@@ -391,7 +396,7 @@ __device__ __forceinline__ IpmOutcome ipm_solve_segment(int li, const double (&w
       saved = true;
     }
     // Every segment of the warp has to leave the loop together.
-    if (__all_sync(0xffffffffu, done) || it == prm.max_iters) break;
+    if (__all_sync(lanes, done) || it == prm.max_iters) break;
     if (!done) ++iters;
     if (told_to_stop()) break;
 
@@ -412,7 +417,7 @@ __device__ __forceinline__ IpmOutcome ipm_solve_segment(int li, const double (&w
       double held[D];
 #pragma unroll
       for (int d = 0; d < D; ++d) {
-        held[d] = seg_shfl<GP>(cw[d], src[d]);
+        held[d] = seg_shfl<GP>(lanes, cw[d], src[d]);
         diag += cw[d] + held[d];
       }
 #pragma unroll
@@ -430,8 +435,8 @@ __device__ __forceinline__ IpmOutcome ipm_solve_segment(int li, const double (&w
     if (told_to_stop()) break;
     // ---- factorisation -------------------------------------------------------------------
     Ldl8 dense;
-    if constexpr (GP == 8) ldl8_factor(row, dense);
-    else ldl_factor_rows<GP>(row, li);
+    if constexpr (GP == 8) ldl8_factor(lanes, row, dense);
+    else ldl_factor_rows<GP>(lanes, row, li);
 
     // ---- predictor (pass 0) and corrector (pass 1) share one body ------------------------
     // Pass 0 also solves N b = 1 for the border column that carries sum(dy) = r_t.
@@ -456,47 +461,47 @@ __device__ __forceinline__ IpmOutcome ipm_solve_segment(int li, const double (&w
         r_qv[d] = sm - q[d] * v[d] - dq[d] * dv[d];
         rd_t[d] = r_d[d] + r_zf[d] * inv_f[d] - (r_qv[d] - q[d] * r_u[d]) * inv_v[d];
         const double wx = w[d] * theta[d] * rd_t[d];
-        acc += wx - seg_shfl<GP>(wx, src[d]);
+        acc += wx - seg_shfl<GP>(lanes, wx, src[d]);
       }
       double a = acc - r_p + r_sy * inv_y;
       if constexpr (GP == 8) {
-        a = ldl8_solve(dense, li, a);
-        if (pass == 0) border = ldl8_solve(dense, li, 1.0);
+        a = ldl8_solve(lanes, dense, li, a);
+        if (pass == 0) border = ldl8_solve(lanes, dense, li, 1.0);
       } else {
         // One instantiation serves both passes (pass 1 carries a dummy second right-hand
         // side): at GP = 32 the unrolled iteration body is near the instruction cache's size
         // and a second copy of the substitution code costs more than the wasted FMAs.
         double b2 = pass == 0 ? 1.0 : 0.0;
-        ldl_solve_rows<GP, 2>(row, li, a, b2);
+        ldl_solve_rows<GP, 2>(lanes, row, li, a, b2);
         if (pass == 0) border = b2;
       }
       if (told_to_stop()) {
         halted = true;
         break;
       }
-      if (pass == 0) inv_border_sum = fast_rcp(seg_sum<GP>(border));
-      dt = (seg_sum<GP>(a) - r_t) * inv_border_sum;
+      if (pass == 0) inv_border_sum = fast_rcp(seg_sum<GP>(lanes, border));
+      dt = (seg_sum<GP>(lanes, a) - r_t) * inv_border_sum;
       dy = a - dt * border;
       ds = (r_sy - s * dy) * inv_y;
       float rp = ratio_to_bound(s, ds), rd = ratio_to_bound(y, dy);
 #pragma unroll
       for (int d = 0; d < D; ++d) {
-        df[d] = theta[d] * (rd_t[d] - w[d] * (dy - seg_shfl<GP>(dy, dst[d])));
+        df[d] = theta[d] * (rd_t[d] - w[d] * (dy - seg_shfl<GP>(lanes, dy, dst[d])));
         dv[d] = r_u[d] - df[d];
         dz[d] = (r_zf[d] - z[d] * df[d]) * inv_f[d];
         dq[d] = (r_qv[d] - q[d] * dv[d]) * inv_v[d];
         rp = fminf(rp, fminf(ratio_to_bound(f[d], df[d]), ratio_to_bound(v[d], dv[d])));
         rd = fminf(rd, fminf(ratio_to_bound(z[d], dz[d]), ratio_to_bound(q[d], dq[d])));
       }
-      apf = seg_minf<GP>(rp);
-      adf = seg_minf<GP>(rd);
+      apf = seg_minf<GP>(lanes, rp);
+      adf = seg_minf<GP>(lanes, rd);
       if (pass == 0) {  // centring parameter from the affine step
         const double ap = fmin((double)apf, 1.0), ad = fmin((double)adf, 1.0);
         double comp_aff = (s + ap * ds) * (y + ad * dy);
 #pragma unroll
         for (int d = 0; d < D; ++d)
           comp_aff += (z[d] + ad * dz[d]) * (f[d] + ap * df[d]) + (q[d] + ad * dq[d]) * (v[d] + ap * dv[d]);
-        const double ratio = fmin(fmax(seg_sum<GP>(comp_aff) * inv_mu, 0.0), 1.0);
+        const double ratio = fmin(fmax(seg_sum<GP>(lanes, comp_aff) * inv_mu, 0.0), 1.0);
         sm = ratio * ratio * ratio * mu;
       }
     }
@@ -522,7 +527,7 @@ __device__ __forceinline__ IpmOutcome ipm_solve_segment(int li, const double (&w
     finite = finite && (f[d] == f[d]) && fabs(f[d]) < 1e300;
     f_out[d] = fmin(fmax(f[d], 0.0), 1.0);
   }
-  finite = seg_max<GP>(finite ? 0.0 : 1.0) == 0.0;
+  finite = seg_max<GP>(lanes, finite ? 0.0 : 1.0) == 0.0;
   if (!finite) {
 #pragma unroll
     for (int d = 0; d < D; ++d) f_out[d] = 0.5;
@@ -548,8 +553,8 @@ template <int GP, int D>
 __device__ __noinline__ IpmOutcome ipm_solve_segment_ool(int li, const double (&w_in)[D], double fixed,
                                                          const int (&src)[D], const int (&dst)[D],
                                                          const IpmParams prm, double (&f_out)[D], double* anchor,
-                                                         int* anchor_valid) {
-  return ipm_solve_segment<GP, D>(li, w_in, fixed, src, dst, prm, f_out, anchor, anchor_valid);
+                                                         int* anchor_valid, const unsigned lanes) {
+  return ipm_solve_segment<GP, D>(li, w_in, fixed, src, dst, prm, f_out, anchor, anchor_valid, lanes);
 }
 
 }  // namespace lplb

@@ -293,13 +293,21 @@ __device__ __forceinline__ void report_group(const IpmOutcome& res, int grp, Cou
 }
 
 // Warp solver: each warp carries 32/GP groups; a CTA covers `kWarps * 32/GP` groups per round.
-template <int GP, int D>
+// With SKIP_IDLE, segments past the last group do not execute the solve at all, and the lanes
+// of the others are the mask of every warp-level operation in it; without it they run along on
+// zeros.  Which is faster was measured per kernel: inside the fused kernel skipping saves about
+// 1 us per step (one group in a warp of four segments), in the stand-alone solve kernel it
+// costs 1.5-2 us per call.
+template <int GP, int D, bool SKIP_IDLE = false>
 __device__ __forceinline__ void solve_groups(const int* __restrict__ bundle, const Topo& tp, int first_group, int group_stride,
                              IpmParams prm, float* __restrict__ probs, Counter avail, int* status) {
   constexpr int kSeg = 32 / GP;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int seg = lane / GP, li = lane % GP;
   for (int g0 = first_group + warp * kSeg; g0 < tp.n_group; g0 += group_stride) {
+    const int live_segs = SKIP_IDLE ? min(kSeg, tp.n_group - g0) : kSeg;
+    const unsigned lanes = first_lanes(live_segs * GP);
+    if (seg >= live_segs) break;  // g0 + stride is past the last group for these lanes too
     const int grp = g0 + seg;
     const bool live = grp < tp.n_group && li < tp.g;
     double w[D], fixed = 0.0, f[D];
@@ -329,8 +337,8 @@ __device__ __forceinline__ void solve_groups(const int* __restrict__ bundle, con
       anchor_valid = prm.anchor_valid + grp;
     }
     IpmOutcome res;
-    if constexpr (GP == 32) res = ipm_solve_segment_ool<GP, D>(li, w, fixed, src, dst, prm, f, anchor, anchor_valid);
-    else res = ipm_solve_segment<GP, D>(li, w, fixed, src, dst, prm, f, anchor, anchor_valid);
+    if constexpr (GP == 32) res = ipm_solve_segment_ool<GP, D>(li, w, fixed, src, dst, prm, f, anchor, anchor_valid, lanes);
+    else res = ipm_solve_segment<GP, D>(li, w, fixed, src, dst, prm, f, anchor, anchor_valid, lanes);
     if (live) {
 #pragma unroll
       for (int d = 0; d < D; ++d) probs[((size_t)grp * tp.g + li) * D + d] = (float)f[d];
@@ -781,7 +789,8 @@ __device__ __forceinline__ void solver_cta(Topo tp, const Exchange& ex, IpmParam
       // two thousand straight-line instructions per iteration waits for every line of it; here
       // it takes the first of those waits while it has nothing else to do.  Nothing it
       // computes is kept.
-      const int li = lane % GP, g = tp.g;
+      const int li = lane, g = tp.g;
+      if (lane < GP) {
       double w[D], f[D];
       int src[D], dst[D];
 #pragma unroll
@@ -793,7 +802,9 @@ __device__ __forceinline__ void solver_cta(Topo tp, const Exchange& ex, IpmParam
       }
       IpmParams rehearsal{3, 0.0};
       rehearsal.stop = &s_stop;
-      ipm_solve_segment<GP, D>(li, w, li < g ? 3.0 + 0.2 * li : 0.0, src, dst, rehearsal, f);
+      ipm_solve_segment<GP, D>(li, w, li < g ? 3.0 + 0.2 * li : 0.0, src, dst, rehearsal, f, nullptr, nullptr,
+                               first_lanes(GP));
+      }
     }
   }
   team_sync<NT>();
@@ -837,7 +848,7 @@ __device__ __forceinline__ void solver_cta(Topo tp, const Exchange& ex, IpmParam
   if constexpr (GP == 0) {
     solve_groups_block<D>(bundle, tp, 0, 1, prm, probs, avail, status, scratch_after(bundle, tp.n_group * tp.g, tp.d));
   } else {
-    solve_groups<GP, D>(bundle, tp, 0, (NT / 32) * (32 / GP), prm, probs, avail, status);
+    solve_groups<GP, D, true>(bundle, tp, 0, (NT / 32) * (32 / GP), prm, probs, avail, status);
   }
   __threadfence();
   team_sync<NT>();
