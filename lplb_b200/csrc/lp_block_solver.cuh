@@ -354,7 +354,8 @@ __device__ __forceinline__ IpmOutcome ipm_solve_block(const int tid, const int g
   const int n32 = l.gp32, rw = l.r_warps;
   const bool is_row = warp < rw;
   const bool live = tid < g;
-  const double kcomp = (double)(g + 2 * g * D);
+  // one reciprocal each, computed side by side: a double-precision division costs some 300 cycles
+  const double kcomp = (double)(g + 2 * g * D), inv_kcomp = fast_rcp(kcomp), inv_g = fast_rcp((double)g);
   double* mat = sm + l.mat;
   double* wblk = sm + l.wblk;
   int* ctrl = reinterpret_cast<int*>(sm + l.ctrl);
@@ -395,7 +396,7 @@ __device__ __forceinline__ IpmOutcome ipm_solve_block(const int tid, const int g
     total = r[0];
   }
   const bool empty = !(total > 0.0);
-  const double inv_scale = empty ? 0.0 : (double)g / total;
+  const double inv_scale = empty ? 0.0 : (double)g * fast_rcp(total);
   double w[D], base = fixed * inv_scale;
 #pragma unroll
   for (int d = 0; d < D; ++d) {
@@ -425,7 +426,7 @@ __device__ __forceinline__ IpmOutcome ipm_solve_block(const int tid, const int g
 #pragma unroll
   for (int d = 0; d < D; ++d) f[d] = v[d] = 0.5;
   const double load = base + m_times(f, x_wf);
-  double t, s, y = 1.0 / g;
+  double t, s, y = inv_g;
   {
     double r[2] = {live ? load : -1e300, live ? -load : -1e300};
     rows_reduce<2, 3u>(r, l, sm, warp, lane, red_phase);
@@ -434,7 +435,7 @@ __device__ __forceinline__ IpmOutcome ipm_solve_block(const int tid, const int g
     s = live ? t - load : 1.0;
     double r2[1] = {live ? s * y : 0.0};
     rows_reduce<1, 0u>(r2, l, sm, warp, lane, red_phase);
-    const double mu0 = r2[0] / g;
+    const double mu0 = r2[0] * inv_g;
 #pragma unroll
     for (int d = 0; d < D; ++d) z[d] = q[d] = 2.0 * mu0;
   }
@@ -444,7 +445,7 @@ __device__ __forceinline__ IpmOutcome ipm_solve_block(const int tid, const int g
   {
     // The slot is read whether or not it is valid (it is always allocated), so that its loads
     // and the load of the flag are in flight together instead of one behind the other.
-    double fa[D], va[D], za[D], qa[D], sa = 1.0, ya = 1.0 / g, ta = 0.0;
+    double fa[D], va[D], za[D], qa[D], sa = 1.0, ya = inv_g, ta = 0.0;
     const bool slot = live && anchor != nullptr && anchor_valid != nullptr;
 #pragma unroll
     for (int d = 0; d < D; ++d) {
@@ -466,7 +467,7 @@ __device__ __forceinline__ IpmOutcome ipm_solve_block(const int tid, const int g
         za[d] = qa[d] = 1.0;
       }
       sa = 1.0;
-      ya = 1.0 / g;
+      ya = inv_g;
       ta = 0.0;
     }
     const double mfa = m_times(fa, x_rhs);
@@ -520,7 +521,7 @@ __device__ __forceinline__ IpmOutcome ipm_solve_block(const int tid, const int g
       double r[5] = {live ? comp : 0.0, live ? y : 0.0, live ? dual_part + neg_rd : 0.0,
                      live ? base + mf : -1e300, live ? worst_u : 0.0};
       rows_reduce<5, 24u>(r, l, sm, warp, lane, red_phase);
-      mu = r[0] / kcomp;
+      mu = r[0] * inv_kcomp;
       r_t = 1.0 - r[1];
       const double dual = r[2], primal = r[3], infeas = fmax(r[4], fabs(r_t));
       if (!done) {
@@ -716,7 +717,7 @@ __device__ __forceinline__ IpmOutcome ipm_solve_block(const int tid, const int g
   out.iters = iters;
   out.converged = done && finite;
   out.finite = finite;
-  out.gap = empty ? 0.0 : gap / fmax(gap_scale, 1e-300);
+  out.gap = empty ? 0.0 : gap * fast_rcp(fmax(gap_scale, 1e-300));
   return out;
 }
 

@@ -232,6 +232,7 @@ __device__ __forceinline__ IpmOutcome ipm_solve_segment(int li, const double (&w
                                                         int* anchor_valid = nullptr, const unsigned lanes = 0xffffffffu) {
   constexpr double kEta = 0.995;
   constexpr int kComp = GP + 2 * GP * D;
+  constexpr double kInvComp = 1.0 / kComp;
   // Private copies: when this function is not inlined the caller's arrays live in local memory,
   // and every use in the loop would be a load that has to be repeated after each store.
   int src[D], dst[D];
@@ -240,6 +241,24 @@ __device__ __forceinline__ IpmOutcome ipm_solve_segment(int li, const double (&w
     src[d] = src_in[d];
     dst[d] = dst_in[d];
   }
+
+  // The saved iterate is read first, valid or not (the slot is always allocated): its loads and
+  // the load of the flag are in flight while the scaling and the cold start point are computed.
+  double fa[D], va[D], za[D], qa[D], sa = 1.0, ya = 1.0 / GP, ta = 0.0;
+  const bool slot = anchor != nullptr && anchor_valid != nullptr;
+#pragma unroll
+  for (int d = 0; d < D; ++d) {
+    fa[d] = slot ? anchor[d] : 0.5;
+    va[d] = slot ? anchor[D + d] : 0.5;
+    za[d] = slot ? anchor[2 * D + d] : 1.0;
+    qa[d] = slot ? anchor[3 * D + d] : 1.0;
+  }
+  if (slot) {
+    sa = anchor[4 * D];
+    ya = anchor[4 * D + 1];
+    ta = anchor[4 * D + 2];
+  }
+  const bool have = slot && *anchor_valid != 0;
 
   // ---- scale so that the mean rank load is 1 ---------------------------------------
   double mine = fixed;
@@ -251,7 +270,7 @@ __device__ __forceinline__ IpmOutcome ipm_solve_segment(int li, const double (&w
   // through every shuffle below with the rest of the warp, so it is not returned early:
   // it starts out `done`, computes on harmless zeros and reports f = 1 at the end.
   const bool empty = !(total > 0.0);
-  const double inv_scale = empty ? 0.0 : (double)GP / total;
+  const double inv_scale = empty ? 0.0 : (double)GP * fast_rcp(total);
   double w[D], base = fixed * inv_scale;
 #pragma unroll
   for (int d = 0; d < D; ++d) {
@@ -293,23 +312,6 @@ __device__ __forceinline__ IpmOutcome ipm_solve_segment(int li, const double (&w
   // The decision is taken per segment; lanes without a slot (padding) follow their segment.
   bool cold = true;
   {
-    // The slot is read whether or not it is valid (it is always allocated), so that its loads
-    // and the load of the flag are in flight together instead of one behind the other.
-    double fa[D], va[D], za[D], qa[D], sa = 1.0, ya = 1.0 / GP, ta = 0.0;
-    const bool slot = anchor != nullptr && anchor_valid != nullptr;
-#pragma unroll
-    for (int d = 0; d < D; ++d) {
-      fa[d] = slot ? anchor[d] : 0.5;
-      va[d] = slot ? anchor[D + d] : 0.5;
-      za[d] = slot ? anchor[2 * D + d] : 1.0;
-      qa[d] = slot ? anchor[3 * D + d] : 1.0;
-    }
-    if (slot) {
-      sa = anchor[4 * D];
-      ya = anchor[4 * D + 1];
-      ta = anchor[4 * D + 2];
-    }
-    const bool have = slot && *anchor_valid != 0;
     if (!have) {
 #pragma unroll
       for (int d = 0; d < D; ++d) {
@@ -369,7 +371,7 @@ __device__ __forceinline__ IpmOutcome ipm_solve_segment(int li, const double (&w
       neg_rd += fmin(r_d[d], 0.0);
       worst_u = fmax(worst_u, fabs(r_u[d]));
     }
-    const double mu = seg_sum<GP>(lanes, comp) / kComp;
+    const double mu = seg_sum<GP>(lanes, comp) * kInvComp;  // a division costs some 300 cycles per evaluation
     const double r_t = 1.0 - seg_sum<GP>(lanes, y);
     const double primal = seg_max<GP>(lanes, base + mf);
     const double dual = seg_sum<GP>(lanes, dual_part + neg_rd);
@@ -540,7 +542,7 @@ __device__ __forceinline__ IpmOutcome ipm_solve_segment(int li, const double (&w
   out.iters = iters;
   out.converged = done && finite;
   out.finite = finite;
-  out.gap = empty ? 0.0 : gap / fmax(gap_scale, 1e-300);
+  out.gap = empty ? 0.0 : gap * fast_rcp(fmax(gap_scale, 1e-300));
   return out;
 }
 
