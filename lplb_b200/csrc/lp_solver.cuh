@@ -293,57 +293,57 @@ __device__ __forceinline__ IpmOutcome ipm_solve_segment(int li, const double (&w
     return acc;
   };
 
-  // ---- feasible start ------------------------------------------------------------------
-  double f[D], v[D], z[D], q[D];
-#pragma unroll
-  for (int d = 0; d < D; ++d) f[d] = v[d] = 0.5;
-  double load = base + m_times(f);
-  const double lmax = seg_max<GP>(lanes, load), lmin = -seg_max<GP>(lanes, -load);
-  double t = lmax + 0.5 * (lmax - lmin) + 0.05;
-  double s = t - load;
-  double y = 1.0 / GP;
-  {
-    const double mu0 = seg_sum<GP>(lanes, s * y) / GP;
-#pragma unroll
-    for (int d = 0; d < D; ++d) z[d] = q[d] = 2.0 * mu0;
-  }
-
   // ---- warm start from the anchor, if it still fits the data -----------------------------
   // The decision is taken per segment; lanes without a slot (padding) follow their segment.
-  bool cold = true;
-  {
-    if (!have) {
+  if (!have) {
+#pragma unroll
+    for (int d = 0; d < D; ++d) {
+      fa[d] = va[d] = 0.5;
+      za[d] = qa[d] = 1.0;
+    }
+    sa = 1.0;
+    ya = 1.0 / GP;
+    ta = 0.0;
+  }
+  const double mfa = m_times(fa);  // shuffles inside: every lane takes part, with or without a slot
+  const double rp = have ? fabs(ta - base - mfa - sa) : 0.0;
+  // every reduction below is executed by all calling lanes, whatever their segment decides
+  const bool seg_has = seg_max<GP>(lanes, have ? 1.0 : 0.0) > 0.0;
+  const double rp_max = seg_max<GP>(lanes, rp);
+  const double t_anchor = seg_max<GP>(lanes, have ? ta : -1e300);
+  const bool fits = seg_has && !empty && rp_max <= prm.guard;
+  const bool cold = !fits;
+
+  // ---- start point -------------------------------------------------------------------------
+  // The feasible cold start costs four reductions; it is skipped when every calling lane takes
+  // its start from the anchor (the usual case from the second batch on).
+  double f[D], v[D], z[D], q[D], t = t_anchor, s = sa, y = ya;
+#pragma unroll
+  for (int d = 0; d < D; ++d) {
+    f[d] = fa[d];
+    v[d] = va[d];
+    z[d] = za[d];
+    q[d] = qa[d];
+  }
+  if (!__all_sync(lanes, fits && have)) {
+    double cf[D];
+#pragma unroll
+    for (int d = 0; d < D; ++d) cf[d] = 0.5;
+    const double load = base + m_times(cf);
+    const double lmax = seg_max<GP>(lanes, load), lmin = -seg_max<GP>(lanes, -load);
+    const double ct = lmax + 0.5 * (lmax - lmin) + 0.05;
+    const double cs = ct - load;
+    const double mu0 = seg_sum<GP>(lanes, cs * (1.0 / GP)) / GP;
+    if (!(fits && have)) {  // this lane starts cold (its segment does, or it is a padding lane)
 #pragma unroll
       for (int d = 0; d < D; ++d) {
-        fa[d] = va[d] = 0.5;
-        za[d] = qa[d] = 1.0;
+        f[d] = v[d] = 0.5;
+        z[d] = q[d] = 2.0 * mu0;
       }
-      sa = 1.0;
-      ya = 1.0 / GP;
-      ta = 0.0;
+      s = cs;
+      y = 1.0 / GP;
     }
-    const double mfa = m_times(fa);  // shuffles inside: every lane takes part, with or without a slot
-    const double rp = have ? fabs(ta - base - mfa - sa) : 0.0;
-    // every reduction below is executed by all 32 lanes, whatever their segment decides
-    const bool seg_has = seg_max<GP>(lanes, have ? 1.0 : 0.0) > 0.0;
-    const double rp_max = seg_max<GP>(lanes, rp);
-    const double t_anchor = seg_max<GP>(lanes, have ? ta : -1e300);
-    const bool fits = seg_has && !empty && rp_max <= prm.guard;
-    if (fits && have) {
-#pragma unroll
-      for (int d = 0; d < D; ++d) {
-        f[d] = fa[d];
-        v[d] = va[d];
-        z[d] = za[d];
-        q[d] = qa[d];
-      }
-      s = sa;
-      y = ya;
-    }
-    if (fits) {
-      t = t_anchor;
-      cold = false;
-    }
+    if (!fits) t = ct;
   }
   bool saved = false;
 
