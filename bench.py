@@ -110,7 +110,7 @@ def run_ours(args) -> dict:
     n_routed = N_LOGICAL + RED_PER_RANK * EP_SIZE
     extra = {"warm_start": False} if args.cold else {}  # otherwise the library default
     planner = Planner(cube(), n_routed, N_LOGICAL, EP_SIZE, group, device=dev, comm=args.comm, **extra)
-    n_sms = args.n_sms or torch.cuda.get_device_properties(dev).multi_processor_count
+    n_sms = args.n_sms or None  # None: the library picks (one CTA per SM, fewer for small batches)
     pl = planner.n_local_routed_experts
 
     total_steps = args.warmup + args.steps
@@ -330,7 +330,7 @@ def run_ours(args) -> dict:
             "comm": planner.comm,
             "lp_warm_start": planner.warm_start,
             "planner_configuration": "library defaults" if not args.cold and args.comm == "auto" else "non-default flags",
-            "n_sms": n_sms,
+            "n_sms": n_sms or planner._default_ctas(TOKENS_PER_RANK * TOP_K),
             "l2": "256 MiB buffer written between timed iterations",
             "first_step": step0,
             "bias_redraws_inside_timed_steps": redraws_timed,
@@ -490,7 +490,7 @@ def parse_args(argv=None):
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--comm", choices=["auto", "p2p", "nccl", "none"], default="auto")
-    ap.add_argument("--n-sms", type=int, default=0, help="CTAs used by the planner kernels (default: all SMs)")
+    ap.add_argument("--n-sms", type=int, default=0, help="CTAs used by the planner kernels (default: the library picks)")
     ap.add_argument("--cold", action="store_true", help="headline with Planner(warm_start=False) instead of the default")
     ap.add_argument("--first-step", type=int, default=-1, help="number of the first warm-up step (default: chosen "
                     "so that a bias redraw falls inside the timed steps)")
