@@ -87,3 +87,13 @@ def test_dump_lp_exposes_the_solver_inputs():
     assert torch.allclose(d["M"].sum(1), torch.zeros(1, 16, dtype=torch.float64))  # columns sum to zero
     _, t_opt = lp.solve_highs(d["bundle_loads"][0], d["fixed_loads"][0], topology.cube())
     assert abs(float(d["oracle_max_load"][0]) - t_opt) / t_opt < 1e-6
+
+
+def test_default_cta_count_follows_the_batch_size():
+    # one worker CTA per 384 indices beside the solver CTA, at least two CTAs, at most one per SM
+    planner = Planner(topology.cube(), 256 + 16, 256, 8, device="cpu")
+    sms = planner._default_sms()
+    assert planner._default_ctas(0) == 2 and planner._default_ctas(1) == 2
+    assert planner._default_ctas(384 * 3) == min(sms, 4)
+    assert planner._default_ctas(384 * 3 + 1) == min(sms, 5)
+    assert planner._default_ctas(10**9) == sms
